@@ -1,0 +1,688 @@
+// Split-KV decode attention over compressed KV records for sm_100a.
+//
+// Replaces plan_decode / decode_attn / combine of the reference
+// (fragpack/ops/fused_attn_decode.cu:94-163, 214-404, 407-425).
+//
+// Shape of the kernel:
+//  * persistent CTAs (two per SM), each walking a static list of work items
+//    (unit, KV head); a unit is a chunk of `ppc` pages of one sequence;
+//  * per CTA one producer warp streams the items' K and V records as ONE flat
+//    sequence through a ring of shared-memory slots with cp.async.bulk + mbarrier
+//    (full / empty barriers), so the HBM pipeline does not drain at item
+//    boundaries;
+//  * eight consumer warps rebuild K / V bit-exactly in registers as
+//    mma.m16n8k16 A fragments (the record layout is that fragment order) and run
+//    S^T = K Q^T and O^T += V^T P^T with an fp32 online softmax; P is rounded to
+//    BF16 for the second product and the denominator stays fp32, as in the
+//    reference (fused_attn_decode.cu:329-345);
+//  * one consumer barrier per page: probabilities are formed against the
+//    running maximum, and only a page that raises some head's maximum takes a
+//    second barrier to rescale.
+// Every device-side wait is bounded: when it runs out the CTA sets
+// FP_DECODE_WAIT_TIMEOUT in the status word, stops waiting and finishes its
+// control flow, so the context stays usable.
+#include <math.h>
+
+#include "fp_api.h"
+#include "fp_common.cuh"
+
+namespace fpb {
+namespace {
+
+constexpr int kConsumerWarps = 8;
+constexpr int kConsumers = 32 * kConsumerWarps;  // 256 = fragment owners
+constexpr int kThreads = kConsumers + 32;        // + producer warp
+constexpr int kSlots = 4;
+constexpr int kSlotBytes = kCodedMax;            // raw records are read in place
+constexpr int kPRow = 80;                        // bytes per (head, c) row of P, padded
+constexpr int kPBytes = 32 * kPRow;
+constexpr int kPlanThreads = 256;
+
+struct SlotDesc {
+  int64_t addr;  // global address of the record (used for raw records)
+  int32_t vlen;  // rec_len: bytes past the dense part; > kVarCap marks raw
+  int32_t pad;
+};
+
+struct Smem {
+  __align__(128) uint8_t slots[kSlots][kSlotBytes];
+  __align__(16) uint8_t esc[kEscBytes];
+  __align__(16) uint8_t p[2][kPBytes];
+  __align__(16) float ref[2][kConsumerWarps][8];
+  __align__(16) int flag[2][kConsumerWarps];
+  __align__(16) float lsum[kConsumerWarps][8];
+  float mrow[8];
+  // Per item: Q^T B fragments in lane order and the K / V decode tables.
+  __align__(16) uint2 qfrag[8][32];
+  __align__(16) HeadTables tabs[2];
+  SlotDesc desc[kSlots];
+  __align__(8) uint64_t full[kSlots];
+  __align__(8) uint64_t empty[kSlots];
+  int abort;
+};
+
+struct DecodeParams {
+  const uint32_t* q;
+  const int64_t* rec_addr;
+  const int32_t* rec_len;
+  const int32_t* plut;
+  const uint8_t* slut;
+  const int32_t* block_table;
+  const int32_t* seq_lens;
+  const int32_t* plan;
+  float* opart;
+  float* ml;
+  int32_t* status;
+  int64_t q_stride;   // in 32-bit words
+  int64_t bt_stride;  // in entries
+  int kvh, group, units;
+  float scale_log2;
+};
+
+// Plan (int32): [0] pages per chunk, [1] units in use, [2 + 2u] sequence and
+// [3 + 2u] first page of unit u (sequence -1: idle), [2 + 2 units + 2 b] first
+// unit and [.. + 1] chunk count of sequence b, then one spare word and the
+// status word.
+__host__ __device__ __forceinline__ int64_t plan_words(int units) { return 2 + 4LL * units + 2; }
+
+// ---------------------------------------------------------------------------
+// mbarrier / bulk-copy helpers
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_addr(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_addr(bar)) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_addr(bar)),
+               "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ bool mbar_try(uint64_t* bar, uint32_t parity) {
+  uint32_t done;
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+      "selp.u32 %0, 1, 0, p;\n"
+      "}\n"
+      : "=r"(done)
+      : "r"(smem_addr(bar)), "r"(parity)
+      : "memory");
+  return done != 0;
+}
+// Global -> shared bulk copy (no multicast) completing on `bar`.
+__device__ __forceinline__ void bulk_load(void* dst, const void* src, uint32_t bytes,
+                                          uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+      ::"r"(smem_addr(dst)), "l"(src), "r"(bytes), "r"(smem_addr(bar))
+      : "memory");
+}
+__device__ __forceinline__ void prefetch_l2(const void* src, uint32_t bytes) {
+  asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(src), "r"(bytes) : "memory");
+}
+
+constexpr long long kWaitCycles = 4000000000LL;  // about two seconds
+
+// Waits for `parity` of `bar` to complete, at most kWaitCycles.  Returns false
+// (and raises the CTA's abort flag) when the wait ran out or the CTA had
+// already given up.
+__device__ __noinline__ bool wait_slow(uint64_t* bar, uint32_t parity, volatile int* abort,
+                                       int32_t* status) {
+  const long long t0 = clock64();
+  for (;;) {
+#pragma unroll 1
+    for (int i = 0; i < 64; ++i)
+      if (mbar_try(bar, parity)) return true;
+    if (*abort) return false;
+    if (clock64() - t0 > kWaitCycles) {
+      *abort = 1;
+      atomicOr(status, FP_DECODE_WAIT_TIMEOUT);
+      return false;
+    }
+  }
+}
+__device__ __forceinline__ bool bounded_wait(uint64_t* bar, uint32_t parity, volatile int* abort,
+                                             int32_t* status) {
+  if (mbar_try(bar, parity)) return true;
+  return wait_slow(bar, parity, abort, status);
+}
+
+__device__ __forceinline__ void consumer_barrier() {
+  asm volatile("bar.sync 1, %0;" ::"n"(kConsumers) : "memory");
+}
+
+// d += A B, one m16n8k16 BF16 tile with fp32 accumulation.
+__device__ __forceinline__ void mma_16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2,
+                                          uint32_t a3, uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 "
+      "{%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+// ---------------------------------------------------------------------------
+// Work items.  Both roles enumerate the same items in the same order.
+// ---------------------------------------------------------------------------
+struct Item {
+  int unit, head, seq_index, first_page, pages, seq_len;
+};
+
+__device__ __forceinline__ bool load_item(const DecodeParams& p, int item, Item& it) {
+  it.unit = item / p.kvh;
+  it.head = item - it.unit * p.kvh;
+  it.seq_index = p.plan[2 + 2 * it.unit];
+  if (it.seq_index < 0) return false;
+  it.first_page = p.plan[3 + 2 * it.unit];
+  it.seq_len = p.seq_lens[it.seq_index];
+  const int total = (it.seq_len + 127) >> 7;
+  it.pages = max(0, min(total, it.first_page + p.plan[0]) - it.first_page);
+  return it.pages > 0;
+}
+
+// ---------------------------------------------------------------------------
+// Producer warp
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ void produce(const DecodeParams& p, Smem& sm) {
+  const int lane = threadIdx.x & 31;
+  volatile int* abort = &sm.abort;
+  const int n_items = p.plan[1] * p.kvh;
+  uint32_t r = 0;  // records issued so far
+  for (int item = blockIdx.x; item < n_items; item += gridDim.x) {
+    Item it;
+    if (!load_item(p, item, it)) continue;
+    const int32_t* bt = p.block_table + (int64_t)it.seq_index * p.bt_stride + it.first_page;
+    for (int base = 0; base < it.pages; base += 32) {
+      const int page = base + lane;
+      int64_t addr_k = 0, addr_v = 0;
+      int32_t len_k = 0, len_v = 0;
+      if (page < it.pages) {
+        const int64_t idx = ((int64_t)bt[page] * 2) * p.kvh + it.head;
+        addr_k = p.rec_addr[idx];
+        addr_v = p.rec_addr[idx + p.kvh];
+        len_k = p.rec_len[idx];
+        len_v = p.rec_len[idx + p.kvh];
+      }
+      const int count = min(32, it.pages - base);
+      for (int j = 0; j < 2 * count; ++j) {
+        const int src = j >> 1;
+        const int64_t addr = __shfl_sync(0xffffffffu, (j & 1) ? addr_v : addr_k, src);
+        const int32_t vlen = __shfl_sync(0xffffffffu, (j & 1) ? len_v : len_k, src);
+        const uint32_t slot = r % kSlots, use = r / kSlots;
+        if (lane == 0) {
+          bool ok = true;
+          if (use > 0) ok = bounded_wait(&sm.empty[slot], (use - 1) & 1, abort, p.status);
+          if (ok) {
+            sm.desc[slot].addr = addr;
+            sm.desc[slot].vlen = vlen;
+            if (vlen > kVarCap || vlen < kHeaderBytes) {
+              // Raw records are read in place by the consumers; warm the L2.
+              prefetch_l2(reinterpret_cast<const void*>(addr), kRawRecord);
+              mbar_arrive(&sm.full[slot]);
+            } else {
+              const uint32_t bytes = (uint32_t)(kDenseBytes + (vlen & ~15));
+              mbar_expect_tx(&sm.full[slot], bytes);
+              bulk_load(sm.slots[slot], reinterpret_cast<const void*>(addr), bytes,
+                        &sm.full[slot]);
+            }
+          }
+        }
+        ++r;
+        __syncwarp();
+        if (*abort) return;  // uniform: lane 0's write is ordered by the warp sync
+      }
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------
+// Consumer warps
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ void consume(const DecodeParams& p, Smem& sm) {
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int g = lane >> 2, c = lane & 3;
+  volatile int* abort = &sm.abort;
+  const int n_items = p.plan[1] * p.kvh;
+  uint32_t r = 0;      // records consumed so far (matches the producer's count)
+  uint32_t pages = 0;  // pages consumed so far: parity selects the P / ref buffers
+
+  auto release = [&](uint32_t slot) {
+    __syncwarp();
+    if (lane == 0) mbar_arrive(&sm.empty[slot]);
+  };
+
+  for (int item = blockIdx.x; item < n_items; item += gridDim.x) {
+    Item it;
+    if (!load_item(p, item, it)) continue;
+    // Stage this item's Q^T B fragments (head g, zero beyond the group; dims
+    // 16 st + 2 c and + 8) and decode tables in shared memory.  The barrier
+    // that closed the previous item ordered its last reads before these writes.
+    {
+      const uint32_t* q =
+          p.q + (int64_t)it.seq_index * p.q_stride + (int64_t)(it.head * p.group + g) * 64;
+      const int st = warp;
+      sm.qfrag[st][lane] = g < p.group ? make_uint2(q[8 * st + c], q[8 * st + 4 + c])
+                                        : make_uint2(0u, 0u);
+      if (tid < 2) sm.tabs[tid] = load_tables(p.plut, p.slut, tid * p.kvh + it.head);
+    }
+    consumer_barrier();
+    // Thread (g, c) of warp w holds S[head 2c+e][token 16w + 8jj + g] in
+    // s[2jj+e] and O[head 2c+e][dim 16w + 8jj + g] in o[2jj+e].
+    float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+    float o[4] = {0.f, 0.f, 0.f, 0.f};
+
+    for (int i = 0; i < it.pages; ++i, ++pages) {
+      const int buf = pages & 1;
+      const int page_tok0 = (it.first_page + i) * 128;
+      // ---------------- K: S^T = K Q^T
+      float s[4] = {0.f, 0.f, 0.f, 0.f};
+      {
+        const uint32_t slot = r % kSlots;
+        bounded_wait(&sm.full[slot], (r / kSlots) & 1, abort, p.status);
+        const int32_t vlen = sm.desc[slot].vlen;
+        auto qk = [&](int st, const uint32_t (&w)[4]) {
+          const uint2 qb = sm.qfrag[st][lane];
+          mma_16816(s, w[0], w[2], w[1], w[3], qb.x, qb.y);
+        };
+        if (vlen > kVarCap || vlen < kHeaderBytes) {
+          const uint8_t* rec = reinterpret_cast<const uint8_t*>(sm.desc[slot].addr);
+          release(slot);
+          raw_record_words(rec, tid, qk);
+        } else {
+          coded_record_words(sm.slots[slot], sm.tabs[0], sm.esc, tid, [&] { release(slot); }, qk);
+        }
+        ++r;
+      }
+      // ---------------- softmax bookkeeping
+      const int tok = page_tok0 + 16 * warp + g;
+      const bool in0 = tok < it.seq_len, in1 = tok + 8 < it.seq_len;
+      s[0] = in0 ? s[0] * p.scale_log2 : -INFINITY;
+      s[1] = in0 ? s[1] * p.scale_log2 : -INFINITY;
+      s[2] = in1 ? s[2] * p.scale_log2 : -INFINITY;
+      s[3] = in1 ? s[3] * p.scale_log2 : -INFINITY;
+      float mx[2] = {fmaxf(s[0], s[2]), fmaxf(s[1], s[3])};
+#pragma unroll
+      for (int x = 4; x < 32; x <<= 1) {
+        mx[0] = fmaxf(mx[0], __shfl_xor_sync(0xffffffffu, mx[0], x));
+        mx[1] = fmaxf(mx[1], __shfl_xor_sync(0xffffffffu, mx[1], x));
+      }
+      const bool raised = __any_sync(0xffffffffu, mx[0] > m_run[0] || mx[1] > m_run[1]);
+      if (g == 0) *reinterpret_cast<float2*>(&sm.ref[buf][warp][2 * c]) = make_float2(mx[0], mx[1]);
+      if (lane == 0) sm.flag[buf][warp] = raised;
+      // P rows: (head, c') holds, for every k-step st, the two B words
+      // (tokens 16 st + 2 c' + {0,1} and + 8) of the second product.
+      uint8_t* prow = sm.p[buf];
+      auto put_p = [&](const float (&pv)[4]) {
+#pragma unroll
+        for (int jj = 0; jj < 2; ++jj)
+#pragma unroll
+          for (int e = 0; e < 2; ++e) {
+            const int head = 2 * c + e;
+            *reinterpret_cast<__nv_bfloat16*>(prow + (head * 4 + (g >> 1)) * kPRow +
+                                              4 * (2 * warp + jj) + 2 * (g & 1)) =
+                __float2bfloat16_rn(pv[2 * jj + e]);
+          }
+      };
+      float pv[4];
+      if (!raised) {
+#pragma unroll
+        for (int x = 0; x < 4; ++x) pv[x] = fast_exp2(s[x] - m_run[x & 1]);
+        put_p(pv);
+      }
+      consumer_barrier();
+      {
+        const int4 f0 = *reinterpret_cast<const int4*>(&sm.flag[buf][0]);
+        const int4 f1 = *reinterpret_cast<const int4*>(&sm.flag[buf][4]);
+        if (f0.x | f0.y | f0.z | f0.w | f1.x | f1.y | f1.z | f1.w) {
+          // Some head's maximum rose: rescale the state, redo P against it.
+          float m_new[2] = {m_run[0], m_run[1]};
+#pragma unroll
+          for (int w = 0; w < kConsumerWarps; ++w) {
+            const float2 t = *reinterpret_cast<const float2*>(&sm.ref[buf][w][2 * c]);
+            m_new[0] = fmaxf(m_new[0], t.x);
+            m_new[1] = fmaxf(m_new[1], t.y);
+          }
+#pragma unroll
+          for (int e = 0; e < 2; ++e) {
+            // A head with no valid token yet keeps -inf; use 0 as its reference.
+            const float base = m_new[e] == -INFINITY ? 0.f : m_new[e];
+            const float alpha = fast_exp2(m_run[e] - base);
+            l_run[e] *= alpha;
+            o[e] *= alpha;
+            o[2 + e] *= alpha;
+            pv[e] = fast_exp2(s[e] - base);
+            pv[2 + e] = fast_exp2(s[2 + e] - base);
+            m_run[e] = m_new[e];
+          }
+          put_p(pv);
+          consumer_barrier();
+        }
+      }
+      l_run[0] += pv[0] + pv[2];
+      l_run[1] += pv[1] + pv[3];
+
+      // ---------------- V: O^T += V^T P^T
+      {
+        const uint32_t slot = r % kSlots;
+        bounded_wait(&sm.full[slot], (r / kSlots) & 1, abort, p.status);
+        const int32_t vlen = sm.desc[slot].vlen;
+        const uint4* pw = reinterpret_cast<const uint4*>(prow + (g * 4 + c) * kPRow);
+        uint4 b;
+        // Tokens of a partial last page beyond the sequence are forced to
+        // zero so that stale bytes of an open block cannot reach the output.
+        const int rem = it.seq_len - page_tok0;
+        auto pvm = [&](int st, const uint32_t (&w)[4]) {
+          uint32_t a[4] = {w[0], w[1], w[2], w[3]};
+          if (rem < 128) {
+#pragma unroll
+            for (int x = 0; x < 4; ++x) {
+              const int t0 = 16 * st + 8 * (x & 1) + 2 * c;
+              if (t0 >= rem) a[x] = 0u;
+              else if (t0 + 1 >= rem) a[x] &= 0xffffu;
+            }
+          }
+          if ((st & 1) == 0) b = pw[st >> 1];
+          mma_16816(o, a[0], a[2], a[1], a[3], (st & 1) ? b.z : b.x, (st & 1) ? b.w : b.y);
+        };
+        if (vlen > kVarCap || vlen < kHeaderBytes) {
+          const uint8_t* rec = reinterpret_cast<const uint8_t*>(sm.desc[slot].addr);
+          release(slot);
+          raw_record_words(rec, tid, pvm);
+        } else {
+          coded_record_words(sm.slots[slot], sm.tabs[1], sm.esc, tid, [&] { release(slot); }, pvm);
+        }
+        ++r;
+      }
+    }
+
+    // ---------------- partial result of this (unit, head)
+    const int64_t row0 = ((int64_t)it.head * p.units + it.unit) * 8;
+#pragma unroll
+    for (int jj = 0; jj < 2; ++jj)
+#pragma unroll
+      for (int e = 0; e < 2; ++e)
+        p.opart[(row0 + 2 * c + e) * 128 + 16 * warp + 8 * jj + g] = o[2 * jj + e];
+    float l[2] = {l_run[0], l_run[1]};
+#pragma unroll
+    for (int x = 4; x < 32; x <<= 1) {
+      l[0] += __shfl_xor_sync(0xffffffffu, l[0], x);
+      l[1] += __shfl_xor_sync(0xffffffffu, l[1], x);
+    }
+    if (g == 0) *reinterpret_cast<float2*>(&sm.lsum[warp][2 * c]) = make_float2(l[0], l[1]);
+    if (warp == 0 && g == 0)
+      *reinterpret_cast<float2*>(&sm.mrow[2 * c]) = make_float2(m_run[0], m_run[1]);
+    consumer_barrier();
+    if (tid < 8) {
+      float sum = 0.f;
+#pragma unroll
+      for (int w = 0; w < kConsumerWarps; ++w) sum += sm.lsum[w][tid];
+      p.ml[(row0 + tid) * 2] = sm.mrow[tid];
+      p.ml[(row0 + tid) * 2 + 1] = sum;
+    }
+    // The next item's first page barrier orders these reads before the next
+    // writes of lsum / mrow.
+  }
+}
+
+__global__ void __launch_bounds__(kThreads, 2) decode_attn_kernel(DecodeParams p) {
+  extern __shared__ __align__(128) uint8_t dyn[];
+  Smem& sm = *reinterpret_cast<Smem*>(dyn);
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kSlots; ++s) {
+      mbar_init(&sm.full[s], 1);
+      mbar_init(&sm.empty[s], kConsumerWarps);
+    }
+    sm.abort = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncthreads();
+  if (threadIdx.x >= kConsumers) {
+    produce(p, sm);
+  } else {
+    consume(p, sm);
+  }
+  // Nothing may still be writing this CTA's shared memory when it exits: on
+  // the normal path every issued copy has been consumed; after a timeout give
+  // the copies in flight a bounded chance to land.
+  __syncthreads();
+  if (sm.abort && threadIdx.x == 0) {
+    const long long t0 = clock64();
+    while (clock64() - t0 < 20000000LL) {
+    }
+  }
+}
+
+// Merges the chunk partials of every sequence into BF16 out[B, H * group, 128].
+// Rows without context (CUDA-graph padding) become zeros.
+__global__ void __launch_bounds__(128)
+combine_kernel(const float* opart, const float* ml, const int32_t* plan, __nv_bfloat16* out,
+               int64_t out_stride, int units, int group) {
+  const int b = blockIdx.x, d = threadIdx.x;
+  const int head = blockIdx.y / group, gq = blockIdx.y % group;
+  const int first = plan[2 + 2 * units + 2 * b], chunks = plan[3 + 2 * units + 2 * b];
+  const int64_t base = (int64_t)head * units + first;
+  float top = -INFINITY;
+  for (int s = 0; s < chunks; ++s) top = fmaxf(top, ml[((base + s) * 8 + gq) * 2]);
+  float den = 0.f, acc = 0.f;
+  if (top != -INFINITY) {
+    for (int s = 0; s < chunks; ++s) {
+      const int64_t row = (base + s) * 8 + gq;
+      const float w = exp2f(ml[row * 2] - top);
+      den += w * ml[row * 2 + 1];
+      acc += w * opart[row * 128 + d];
+    }
+  }
+  out[(int64_t)b * out_stride + (int64_t)blockIdx.y * 128 + d] =
+      __float2bfloat16(den > 0.f ? acc / den : 0.f);
+}
+
+// ---------------------------------------------------------------------------
+// Planner: one CTA, once per step.  Picks the chunk length (pages per unit)
+// that minimises the static schedule's makespan on `slots` resident CTAs and
+// maps units to (sequence, first page).
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ int block_reduce_sum(int v, int* scratch) {
+#pragma unroll
+  for (int x = 16; x; x >>= 1) v += __shfl_xor_sync(0xffffffffu, v, x);
+  __syncthreads();
+  if ((threadIdx.x & 31) == 0) scratch[threadIdx.x >> 5] = v;
+  __syncthreads();
+  int t = 0;
+#pragma unroll
+  for (int w = 0; w < kPlanThreads / 32; ++w) t += scratch[w];
+  return t;
+}
+__device__ __forceinline__ int block_reduce_max(int v, int* scratch) {
+#pragma unroll
+  for (int x = 16; x; x >>= 1) v = max(v, __shfl_xor_sync(0xffffffffu, v, x));
+  __syncthreads();
+  if ((threadIdx.x & 31) == 0) scratch[threadIdx.x >> 5] = v;
+  __syncthreads();
+  int t = 0;
+#pragma unroll
+  for (int w = 0; w < kPlanThreads / 32; ++w) t = max(t, scratch[w]);
+  return t;
+}
+
+__global__ void __launch_bounds__(kPlanThreads)
+plan_kernel(const int32_t* seq_lens, int32_t* plan, int batch, int units, int kvh, int slots) {
+  __shared__ int scratch[kPlanThreads / 32];
+  __shared__ unsigned long long best;
+  __shared__ int warp_total[kPlanThreads / 32];
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  int total = 0, longest = 0, active = 0;
+  for (int b = tid; b < batch; b += kPlanThreads) {
+    const int n = (seq_lens[b] + 127) >> 7;
+    total += n;
+    longest = max(longest, n);
+    active += n > 0;
+  }
+  total = block_reduce_sum(total, scratch);
+  longest = block_reduce_max(longest, scratch);
+  active = block_reduce_sum(active, scratch);
+  // Each padding row gives back the unit reserved for it.
+  const int capacity = max(1, units - batch + active);
+  if (tid == 0) best = ~0ull;
+  __syncthreads();
+  // Candidate k cuts the longest sequence into k chunks.
+  {
+    const int ppc = max(1, (longest + tid) / (tid + 1));
+    const float inv = 1.0f / (float)ppc;
+    int chunks = 0;
+    for (int b = 0; b < batch; ++b) {
+      // ceil(pages / ppc) without an integer division: estimate, then correct.
+      const int up = ((seq_lens[b] + 127) >> 7) + ppc - 1;
+      int q = (int)((float)up * inv);
+      if (q * ppc > up) --q;
+      if ((q + 1) * ppc <= up) ++q;
+      chunks += q;
+    }
+    if (chunks <= capacity) {
+      const long long items = (long long)chunks * kvh;
+      const long long rounds = max(1LL, (items + slots - 1) / slots);
+      // Per item: ppc pages plus about three quarters of a page of start-up.
+      const unsigned long long cost = (unsigned long long)(rounds * (4LL * ppc + 3));
+      // Ties go to the longer chunk (fewer partial results).
+      atomicMin(&best, (cost << 20) | (unsigned long long)(0xfffff - ppc));
+    }
+  }
+  __syncthreads();
+  const int ppc = (int)(0xfffff - (best & 0xfffff));
+
+  int32_t* seq_plan = plan + 2 + 2 * units;
+  int used = 0;
+  for (int base = 0; base < batch; base += kPlanThreads) {
+    const int b = base + tid;
+    const int chunks = b < batch ? (((seq_lens[b] + 127) >> 7) + ppc - 1) / ppc : 0;
+    const int before = warp_exclusive_sum(chunks, lane);
+    if (lane == 31) warp_total[warp] = before + chunks;
+    __syncthreads();
+    int first = used + before, tile = 0;
+#pragma unroll
+    for (int w = 0; w < kPlanThreads / 32; ++w) {
+      if (w < warp) first += warp_total[w];
+      tile += warp_total[w];
+    }
+    if (b < batch) {
+      seq_plan[2 * b] = first;
+      seq_plan[2 * b + 1] = chunks;
+      for (int s = 0; s < chunks; ++s) {
+        plan[2 + 2 * (first + s)] = b;
+        plan[3 + 2 * (first + s)] = s * ppc;
+      }
+    }
+    used += tile;
+    __syncthreads();
+  }
+  for (int u = used + tid; u < units; u += kPlanThreads) plan[2 + 2 * u] = -1;
+  if (tid == 0) {
+    plan[0] = ppc;
+    plan[1] = used;
+    plan[plan_words(units) - 2] = 0;
+    plan[plan_words(units) - 1] = 0;  // status
+  }
+}
+
+int device_sms() {
+  static int cached[64] = {0};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+  if (cached[dev] == 0) {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0)
+      n = 148;
+    cached[dev] = n;
+  }
+  return cached[dev];
+}
+
+}  // namespace
+}  // namespace fpb
+
+using namespace fpb;
+
+extern "C" {
+
+int fp_decode_workspace(int32_t kv_heads, int32_t units, int64_t* opart_elems, int64_t* ml_elems,
+                        int64_t* plan_elems) {
+  FP_REQUIRE(kv_heads > 0 && units > 0, "bad workspace geometry");
+  const int64_t rows = (int64_t)kv_heads * units * 8;
+  if (opart_elems) *opart_elems = rows * 128;
+  if (ml_elems) *ml_elems = rows * 2;
+  if (plan_elems) *plan_elems = plan_words(units);
+  return FP_OK;
+}
+
+int fp_fused_decode(const void* q, int64_t q_stride, const int64_t* rec_addr,
+                    const int32_t* rec_len, const int32_t* plut, const uint8_t* slut,
+                    const int32_t* block_table, int64_t bt_stride, const int32_t* seq_lens,
+                    float* opart, int64_t opart_elems, float* ml, int64_t ml_elems, int32_t* plan,
+                    int64_t plan_elems, void* out, int64_t out_stride, int32_t batch,
+                    int32_t kv_heads, int32_t group, int32_t units, int32_t replan, float scale,
+                    int32_t num_sms, void* stream) {
+  if (batch == 0) return FP_OK;
+  FP_REQUIRE(batch > 0 && kv_heads > 0, "bad batch %d / kv_heads %d", batch, kv_heads);
+  FP_REQUIRE(group == 1 || group == 2 || group == 4 || group == 8,
+             "query group %d must be 1, 2, 4 or 8", group);
+  FP_REQUIRE(units >= batch, "decode needs at least one unit per sequence");
+  FP_REQUIRE(q && rec_addr && rec_len && plut && slut && block_table && seq_lens && opart && ml &&
+                 plan && out,
+             "null decode argument");
+  FP_REQUIRE(q_stride % 2 == 0 && reinterpret_cast<uintptr_t>(q) % 4 == 0,
+             "q rows must be 4-byte aligned");
+  FP_REQUIRE(reinterpret_cast<uintptr_t>(slut) % 16 == 0, "slut must be 16-byte aligned");
+  FP_REQUIRE(opart_elems >= (int64_t)kv_heads * units * 8 * 128 &&
+                 ml_elems >= (int64_t)kv_heads * units * 16,
+             "decode workspace too small");
+  FP_REQUIRE(plan_elems >= plan_words(units), "decode plan must hold %lld int32",
+             (long long)plan_words(units));
+  const int sms = num_sms > 0 ? num_sms : device_sms();
+  const int slots = 2 * sms;
+  cudaStream_t st = (cudaStream_t)stream;
+  if (replan) {
+    plan_kernel<<<1, kPlanThreads, 0, st>>>(seq_lens, plan, batch, units, kv_heads, slots);
+    FP_LAUNCH_CHECK("plan_kernel");
+  }
+  DecodeParams p;
+  p.q = static_cast<const uint32_t*>(q);
+  p.rec_addr = rec_addr;
+  p.rec_len = rec_len;
+  p.plut = plut;
+  p.slut = slut;
+  p.block_table = block_table;
+  p.seq_lens = seq_lens;
+  p.plan = plan;
+  p.opart = opart;
+  p.ml = ml;
+  p.status = plan + plan_words(units) - 1;
+  p.q_stride = q_stride / 2;
+  p.bt_stride = bt_stride;
+  p.kvh = kv_heads;
+  p.group = group;
+  p.units = units;
+  p.scale_log2 = scale * 1.4426950408889634f;
+  const int smem = (int)sizeof(Smem);
+  if (int rc = cuda_status(cudaFuncSetAttribute(decode_attn_kernel,
+                                                cudaFuncAttributeMaxDynamicSharedMemorySize, smem),
+                           "cudaFuncSetAttribute(decode_attn_kernel)"))
+    return rc;
+  const long long max_items = (long long)units * kv_heads;
+  const int grid = (int)(max_items < slots ? max_items : slots);
+  decode_attn_kernel<<<grid, kThreads, smem, st>>>(p);
+  FP_LAUNCH_CHECK("decode_attn_kernel");
+  combine_kernel<<<dim3(batch, kv_heads * group), 128, 0, st>>>(
+      opart, ml, plan, static_cast<__nv_bfloat16*>(out), out_stride, units, group);
+  FP_LAUNCH_CHECK("combine_kernel");
+  return FP_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,752 @@
+// HBM KV store kernels for sm_100a: step bookkeeping (prepare / commit), the
+// token writer, the block encoder, the prefill decompressor, and the batch
+// codec entry points.  Behaviour follows fragpack/ops/hbm_kv.cu of the
+// reference (cited per kernel); the byte format is attn_page.py's.
+#include <stdarg.h>
+#include <stdio.h>
+
+#include "fp_api.h"
+#include "fp_common.cuh"
+
+namespace fpb {
+
+namespace {
+thread_local char g_error[512] = "";
+}
+
+int fail(int code, const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_error, sizeof g_error, fmt, ap);
+  va_end(ap);
+  return code;
+}
+
+int cuda_status(cudaError_t err, const char* what) {
+  if (err == cudaSuccess) return FP_OK;
+  return fail(FP_ERR_CUDA, "%s: %s", what, cudaGetErrorString(err));
+}
+
+const char* last_error() { return g_error; }
+
+namespace {
+
+enum : int { kTagLive = 0, kTagClose = 1, kTagClaim = 2, kTagCloseOnce = 3 };
+constexpr int kPrepareThreads = 1024;
+
+// Device view of fp_store with the address arithmetic of the staging pools.
+struct StoreView {
+  fp_store s;
+  // Staging record `rec` (= kv * H + head) of staging slot `slot` at `layer`.
+  // Slots below S_p are persistent (one record set per layer); the others are
+  // transient scratch that holds a single layer (hbm_kv.cu:80-84).
+  __device__ __forceinline__ uint8_t* staging(int slot, int layer, int rec) const {
+    const int per = 2 * s.H;
+    if (slot < s.S_p) return s.staging + (((int64_t)slot * s.L + layer) * per + rec) * kRawRecord;
+    return s.scratch + ((int64_t)(slot - s.S_p) * per + rec) * kRawRecord;
+  }
+  __device__ __forceinline__ int64_t table_index(int layer, int block, int rec) const {
+    return ((int64_t)layer * s.NB + block) * 2 * s.H + rec;
+  }
+  // Overflow slots are a bitmap so that encodes and imports on different
+  // streams can allocate concurrently (hbm_kv.cu:86-108).
+  __device__ int overflow_take(uint32_t hint) const {
+    for (int i = 0; i < s.ovf_words; ++i) {
+      const int w = (int)((hint + (uint32_t)i) % (uint32_t)s.ovf_words);
+      uint32_t seen = *reinterpret_cast<volatile uint32_t*>(&s.ovf_bits[w]);
+      while (seen != 0xffffffffu) {
+        const uint32_t bit = 1u << (__ffs(~seen) - 1);
+        const uint32_t before = atomicOr(&s.ovf_bits[w], bit);
+        if (!(before & bit)) return 32 * w + (__ffs(bit) - 1);
+        seen = before | bit;
+      }
+    }
+    return -1;
+  }
+  __device__ __forceinline__ void overflow_give_back(int64_t addr) const {
+    const int64_t base = reinterpret_cast<int64_t>(s.overflow);
+    if (addr < base || addr >= base + s.overflow_records * kRawRecord) return;
+    const int slot = (int)((addr - base) / kRawRecord);
+    atomicAnd(&s.ovf_bits[slot >> 5], ~(1u << (slot & 31)));
+  }
+};
+
+// ---------------------------------------------------------------------------
+// prepare: one CTA.  hbm_kv.cu:110-219 of the reference.
+//   1. blocks not listed live lose their persistent staging slot;
+//   2. blocks receiving offset 127 this step are stamped as closing;
+//   3. blocks receiving offset 0 claim staging: their own slot if they kept
+//      one, a transient slot if they also close this step, else a persistent
+//      slot; with none free the block becomes an heir (transient now, the
+//      slot of a block closing this step at commit);
+//   4. closing blocks that own a slot are listed, each persistent one paired
+//      with a waiting heir;
+//   5. every record of a claimed block points at its staging, overflow slots
+//      it held are returned and its arena page is emptied.
+// ---------------------------------------------------------------------------
+__global__ void __launch_bounds__(kPrepareThreads)
+prepare_kernel(StoreView v, const int64_t* slots, int n_tok, const int32_t* live, int n_live,
+               int32_t step) {
+  const fp_store& s = v.s;
+  const int tid = threadIdx.x;
+  int32_t* tag_live = s.tags + kTagLive * s.NB;
+  int32_t* tag_close = s.tags + kTagClose * s.NB;
+  int32_t* tag_claim = s.tags + kTagClaim * s.NB;
+  int32_t* tag_once = s.tags + kTagCloseOnce * s.NB;
+  if (tid == 0) {
+    s.counters[FP_CTR_TRANSIENT] = 0;
+    s.counters[FP_CTR_CLAIMS] = 0;
+    s.counters[FP_CTR_CLOSES] = 0;
+    s.counters[FP_CTR_HEIRS] = 0;
+    s.counters[FP_CTR_DONORS] = 0;
+  }
+  for (int i = tid; i < n_live; i += kPrepareThreads) {
+    const int b = live[i];
+    if (b >= 0 && b < s.NB) tag_live[b] = step;
+  }
+  __syncthreads();
+
+  for (int b = tid; b < s.NB; b += kPrepareThreads) {
+    const int w = s.wslot[b];
+    if (w < 0) continue;
+    if (w >= s.S_p) {
+      s.wslot[b] = -1;  // transient slots never outlive their step
+    } else if (tag_live[b] != step) {
+      s.wslot[b] = -1;
+      s.free_stack[atomicAdd(&s.counters[FP_CTR_FREE_TOP], 1)] = w;
+    }
+  }
+  for (int i = tid; i < n_tok; i += kPrepareThreads) {
+    const int64_t slot = slots[i];
+    if (slot >= 0 && (slot & 127) == 127) tag_close[slot >> 7] = step;
+  }
+  __syncthreads();
+
+  for (int i = tid; i < n_tok; i += kPrepareThreads) {
+    const int64_t slot = slots[i];
+    if (slot < 0 || (slot & 127) != 0) continue;
+    const int b = (int)(slot >> 7);
+    if (atomicExch(&tag_claim[b], step) == step) continue;  // first token only
+    int w = s.wslot[b];
+    if (w < 0) {
+      const bool closes_now = tag_close[b] == step;
+      if (closes_now) {
+        const int t = atomicAdd(&s.counters[FP_CTR_TRANSIENT], 1);
+        if (t < s.S_t) w = s.S_p + t;
+      }
+      if (w < 0) {
+        const int top = atomicSub(&s.counters[FP_CTR_FREE_TOP], 1) - 1;
+        if (top >= 0) {
+          w = s.free_stack[top];
+        } else {
+          atomicAdd(&s.counters[FP_CTR_FREE_TOP], 1);
+          // No persistent slot: wait in transient scratch for a donor.
+          const int t = closes_now ? s.S_t : atomicAdd(&s.counters[FP_CTR_TRANSIENT], 1);
+          if (t < s.S_t) {
+            w = s.S_p + t;
+            s.claim_list[s.cap + atomicAdd(&s.counters[FP_CTR_HEIRS], 1)] = b;
+          } else {
+            atomicAdd(&s.counters[FP_CTR_ERR_STAGING], 1);
+          }
+        }
+      }
+    }
+    s.wslot[b] = w;
+    if (w >= 0) s.claim_list[atomicAdd(&s.counters[FP_CTR_CLAIMS], 1)] = b;
+  }
+  __syncthreads();
+
+  const int heirs = s.counters[FP_CTR_HEIRS];
+  for (int i = tid; i < n_tok; i += kPrepareThreads) {
+    const int64_t slot = slots[i];
+    if (slot < 0 || (slot & 127) != 127) continue;
+    const int b = (int)(slot >> 7);
+    if (atomicExch(&tag_once[b], step) == step) continue;
+    const int w = s.wslot[b];
+    if (w < 0) continue;
+    const int at = atomicAdd(&s.counters[FP_CTR_CLOSES], 1);
+    s.close_list[at] = b;
+    int heir = -1;
+    if (w < s.S_p && heirs > 0) {
+      const int d = atomicAdd(&s.counters[FP_CTR_DONORS], 1);
+      if (d < heirs) heir = s.claim_list[s.cap + d];
+    }
+    s.close_list[s.cap + at] = heir;
+  }
+  __syncthreads();
+  // An heir left without a donor would lose its KV at commit.
+  if (tid == 0 && s.counters[FP_CTR_DONORS] < heirs)
+    atomicAdd(&s.counters[FP_CTR_ERR_STAGING], heirs - s.counters[FP_CTR_DONORS]);
+
+  const int claims = s.counters[FP_CTR_CLAIMS];
+  const int per_block = s.L * 2 * s.H;
+  for (int x = tid; x < claims * per_block; x += kPrepareThreads) {
+    const int b = s.claim_list[x / per_block];
+    const int within = x % per_block, layer = within / (2 * s.H), rec = within % (2 * s.H);
+    const int64_t idx = v.table_index(layer, b, rec);
+    v.overflow_give_back(s.rec_addr[idx]);
+    s.rec_addr[idx] = reinterpret_cast<int64_t>(v.staging(s.wslot[b], layer, rec));
+    s.rec_len[idx] = kRawVarLen;
+    if (rec == 0) s.fill[(int64_t)layer * s.NB + b] = 0;
+  }
+}
+
+// commit: hbm_kv.cu:431-448.  Closed blocks free their slot or pass it on.
+__global__ void commit_kernel(StoreView v) {
+  const fp_store& s = v.s;
+  const int closes = s.counters[FP_CTR_CLOSES];
+  for (int i = threadIdx.x; i < closes; i += blockDim.x) {
+    const int b = s.close_list[i];
+    const int w = s.wslot[b];
+    const int heir = s.close_list[s.cap + i];
+    if (heir >= 0) {
+      s.wslot[heir] = w;
+    } else if (w >= 0 && w < s.S_p) {
+      s.free_stack[atomicAdd(&s.counters[FP_CTR_FREE_TOP], 1)] = w;
+    }
+    s.wslot[b] = -1;
+  }
+  __syncthreads();
+  // An emptied close list makes a forward without a fresh prepare encode nothing.
+  if (threadIdx.x == 0) s.counters[FP_CTR_CLOSES] = 0;
+}
+
+// ---------------------------------------------------------------------------
+// Token writer: hbm_kv.cu:221-255.  grid = tokens, one warp per KV head slice.
+// Scatters a token's K and V rows into the fragment order of its block's
+// staging record (see fp_common.cuh for the owner layout).
+// ---------------------------------------------------------------------------
+__global__ void __launch_bounds__(256)
+write_kernel(StoreView v, const uint16_t* key, const uint16_t* value, int64_t ks0, int64_t ks1,
+             int64_t vs0, int64_t vs1, const int64_t* slots, int layer) {
+  const fp_store& s = v.s;
+  const int64_t slot = slots[blockIdx.x];
+  if (slot < 0) return;
+  const int block = (int)(slot >> 7), off = (int)(slot & 127);
+  if (block >= s.NB) return;
+  const int w = s.wslot[block];
+  if (w < 0) return;
+  // K: the token is a row of the A fragment; V: it is a column.
+  const int k_warp = off >> 4, k_j = (off >> 3) & 1, k_g = off & 7;
+  const int v_st = off >> 4, v_f = (off >> 3) & 1, v_c = (off >> 1) & 3, v_e = off & 1;
+  for (int x = threadIdx.x; x < s.H * 64; x += blockDim.x) {
+    const int head = x >> 6, pair = x & 63;  // dims 2 pair, 2 pair + 1
+    {
+      const uint32_t val =
+          *reinterpret_cast<const uint32_t*>(key + blockIdx.x * ks0 + head * ks1 + 2 * pair);
+      const int st = pair >> 3, f = (pair >> 2) & 1, c = pair & 3;
+      const int owner = 32 * k_warp + 4 * k_g + c;
+      uint8_t* rec = v.staging(w, layer, head);
+      *reinterpret_cast<uint32_t*>(rec + 16 * (kOwners * st + owner) + 4 * (2 * k_j + f)) = val;
+    }
+    {
+      const uint32_t val =
+          *reinterpret_cast<const uint32_t*>(value + blockIdx.x * vs0 + head * vs1 + 2 * pair);
+      uint8_t* rec = v.staging(w, layer, s.H + head);
+#pragma unroll
+      for (int q = 0; q < 2; ++q) {
+        const int d = 2 * pair + q;
+        const int owner = 32 * (d >> 4) + 4 * (d & 7) + v_c;
+        *reinterpret_cast<uint16_t*>(rec + 16 * (kOwners * v_st + owner) +
+                                     2 * (4 * ((d >> 3) & 1) + 2 * v_f + v_e)) =
+            (uint16_t)(val >> (16 * q));
+      }
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------
+// Block encoder core: attn_page.py:146-209 on one CTA of 256 owners, each
+// holding its eight fragment words.  Bit-exact with the reference encoder.
+// ---------------------------------------------------------------------------
+struct EncodeShared {
+  __align__(16) uint8_t var[kVarCap];
+  uint8_t rank[256];
+  int warp_sum[2][8];
+  uint8_t* dst;
+  int raw;
+};
+
+struct EncodePlan {
+  int var_len;   // variable-region bytes if coded
+  bool codes;    // false: raw fallback (attn_page.py:200-202)
+};
+
+// `place(plan)` runs on thread 0 only and returns where the record goes and
+// whether it must be stored raw (a coded record that no longer fits its page
+// is spilled raw); a null destination drops the record.
+template <typename Place>
+__device__ __forceinline__ void encode_cta(const uint4 (&wd)[8], EncodeShared& sh, int tid,
+                                           Place&& place) {
+  const int lane = tid & 31, warp = tid >> 5;
+  for (int i = tid; i < kVarCap / 16; i += kOwners)
+    reinterpret_cast<uint4*>(sh.var)[i] = make_uint4(0, 0, 0, 0);
+
+  // Classify the 64 scalars: 3-bit primary code into the symbol words, escape
+  // nibbles into a queue (first 16), escape and raw masks.
+  uint32_t sym[6] = {0, 0, 0, 0, 0, 0};
+  uint64_t esc_mask = 0, raw_mask = 0, queue = 0;
+  int n_esc = 0;
+#pragma unroll
+  for (int st = 0; st < 8; ++st) {
+    const uint32_t hi_a = __byte_perm(wd[st].x, wd[st].y, 0x7531);
+    const uint32_t hi_b = __byte_perm(wd[st].z, wd[st].w, 0x7531);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      const int sc = 8 * st + e, gi = sc >> 5, sg = sc & 31;
+      const uint32_t high = ((e < 4 ? hi_a : hi_b) >> (8 * (e & 3))) & 0xffu;
+      const uint32_t r = sh.rank[high];
+      const uint32_t code = min(r, (uint32_t)kPrimaryDirect);
+      if (sg < 24) {
+        sym[3 * gi + (sg >> 3)] |= code << (4 * (sg & 7));
+      } else {
+#pragma unroll
+        for (int k = 0; k < 3; ++k) sym[3 * gi + k] |= ((code >> k) & 1u) << (4 * (sg - 24) + 3);
+      }
+      if (r >= kPrimaryDirect) {
+        const uint32_t nib = r < kTableEntries ? r - kPrimaryDirect : 15u;
+        if (n_esc < 16) queue |= (uint64_t)nib << (4 * n_esc);
+        ++n_esc;
+        esc_mask |= 1ull << sc;
+        if (r >= kTableEntries) raw_mask |= 1ull << sc;
+      }
+    }
+  }
+  const int n_raw = __popcll(raw_mask);
+  const int esc_before = warp_exclusive_sum(n_esc, lane);
+  const int raw_before = warp_exclusive_sum(n_raw, lane);
+  if (lane == 31) {
+    sh.warp_sum[0][warp] = esc_before + n_esc;
+    sh.warp_sum[1][warp] = raw_before + n_raw;
+  }
+  __syncthreads();
+  int esc_at = esc_before, raw_at = raw_before, esc_total = 0, raw_total = 0, raw_worst = 0;
+#pragma unroll
+  for (int w = 0; w < 8; ++w) {
+    const int ew = sh.warp_sum[0][w], rw = sh.warp_sum[1][w];
+    if (w < warp) {
+      esc_at += ew;
+      raw_at += rw;
+    }
+    esc_total += ew;
+    raw_total += rw;
+    raw_worst = max(raw_worst, rw);
+  }
+  const int raw_offset = (kHeaderBytes + ((esc_total + 1) >> 1) + 3) & ~3;
+  EncodePlan plan;
+  plan.var_len = (raw_offset + 4 * raw_total + 15) & ~15;
+  plan.codes = plan.var_len <= kVarCap && raw_worst <= kMaxWarpRaw;
+  if (tid == 0) {
+    bool raw = !plan.codes;
+    sh.dst = place(plan, raw);
+    sh.raw = raw;
+  }
+  __syncthreads();
+  uint8_t* dst = sh.dst;
+  if (dst == nullptr) return;
+  if (sh.raw) {
+#pragma unroll
+    for (int st = 0; st < 8; ++st) reinterpret_cast<uint4*>(dst)[st * kOwners + tid] = wd[st];
+    return;
+  }
+
+  uint32_t* var32 = reinterpret_cast<uint32_t*>(sh.var);
+  if (n_esc > 0 && n_esc <= 16) {
+    // This owner's nibbles are consecutive from nibble `esc_at` of the stream
+    // that starts at byte 48 (word 12).
+    const int word = (kHeaderBytes >> 2) + (esc_at >> 3), shift = 4 * (esc_at & 7);
+    const uint64_t lo = queue << shift;
+    const uint32_t hi = shift ? (uint32_t)(queue >> (64 - shift)) : 0u;
+    if ((uint32_t)lo) atomicOr(&var32[word], (uint32_t)lo);
+    if ((uint32_t)(lo >> 32)) atomicOr(&var32[word + 1], (uint32_t)(lo >> 32));
+    if (hi) atomicOr(&var32[word + 2], hi);
+  }
+  if (n_esc > 16 || n_raw > 0) {
+    // Rare: long escape runs, and raw entries `ordinal | high << 16`.
+    int ordinal = esc_at;
+#pragma unroll
+    for (int st = 0; st < 8; ++st) {
+      const uint32_t hi_a = __byte_perm(wd[st].x, wd[st].y, 0x7531);
+      const uint32_t hi_b = __byte_perm(wd[st].z, wd[st].w, 0x7531);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        const int sc = 8 * st + e;
+        if ((esc_mask >> sc) & 1ull) {
+          const uint32_t high = ((e < 4 ? hi_a : hi_b) >> (8 * (e & 3))) & 0xffu;
+          if (n_esc > 16) {
+            const uint32_t r = sh.rank[high];
+            const uint32_t nib = r < kTableEntries ? r - kPrimaryDirect : 15u;
+            const int bit = 8 * kHeaderBytes + 4 * ordinal;
+            atomicOr(&var32[bit >> 5], nib << (bit & 31));
+          }
+          if ((raw_mask >> sc) & 1ull)
+            var32[(raw_offset >> 2) + raw_at++] = (uint32_t)ordinal | (high << 16);
+          ++ordinal;
+        }
+      }
+    }
+  }
+  if (tid == 0) {
+    var32[0] = esc_total;
+    var32[1] = raw_total;
+    var32[2] = raw_offset;
+    var32[3] = 0;
+    uint16_t* h16 = reinterpret_cast<uint16_t*>(sh.var);
+    int e = 0, r = 0;
+    for (int w = 0; w < 8; ++w) {
+      h16[8 + w] = (uint16_t)e;
+      h16[16 + w] = (uint16_t)r;
+      e += sh.warp_sum[0][w];
+      r += sh.warp_sum[1][w];
+    }
+  }
+  // Dense part: low bytes in four 16-byte chunks, symbols in three 8-byte
+  // chunks, both chunk-major (attn_page.py:272-276).
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const uint4 a = wd[2 * j], b = wd[2 * j + 1];
+    reinterpret_cast<uint4*>(dst)[j * kOwners + tid] =
+        make_uint4(__byte_perm(a.x, a.y, 0x6420), __byte_perm(a.z, a.w, 0x6420),
+                   __byte_perm(b.x, b.y, 0x6420), __byte_perm(b.z, b.w, 0x6420));
+  }
+#pragma unroll
+  for (int m = 0; m < 3; ++m)
+    reinterpret_cast<uint2*>(dst + kLowBytes)[m * kOwners + tid] =
+        make_uint2(sym[2 * m], sym[2 * m + 1]);
+  __syncthreads();
+  for (int i = tid; i < plan.var_len / 16; i += kOwners)
+    reinterpret_cast<uint4*>(dst + kDenseBytes)[i] = reinterpret_cast<const uint4*>(sh.var)[i];
+}
+
+// grid (max_close, 2 H): CTA (i, rec) encodes record `rec` of close_list[i]
+// at `layer` from staging.  hbm_kv.cu:257-429.
+__global__ void __launch_bounds__(kOwners)
+encode_kernel(StoreView v, int layer, uint8_t* arena, int64_t page_bytes, const uint8_t* rank_of) {
+  __shared__ EncodeShared sh;
+  const fp_store& s = v.s;
+  if ((int)blockIdx.x >= s.counters[FP_CTR_CLOSES]) return;
+  const int rec = blockIdx.y, tid = threadIdx.x;
+  const int block = s.close_list[blockIdx.x];
+  uint8_t* src = v.staging(s.wslot[block], layer, rec);
+  const int64_t idx = v.table_index(layer, block, rec);
+  sh.rank[tid] = rank_of[((int64_t)layer * 2 * s.H + rec) * 256 + tid];
+  uint4 wd[8];
+#pragma unroll
+  for (int st = 0; st < 8; ++st) wd[st] = reinterpret_cast<const uint4*>(src)[st * kOwners + tid];
+  // A closing block that donates its slot: the heir's transient record moves
+  // in (each owner overwrites only the words it has just read) and the heir's
+  // table entry follows it.  Attention has already read the transient copy.
+  const int heir = s.close_list[s.cap + blockIdx.x];
+  if (heir >= 0) {
+    const uint4* from = reinterpret_cast<const uint4*>(v.staging(s.wslot[heir], layer, rec));
+#pragma unroll
+    for (int st = 0; st < 8; ++st)
+      reinterpret_cast<uint4*>(src)[st * kOwners + tid] = from[st * kOwners + tid];
+    if (tid == 0) s.rec_addr[v.table_index(layer, heir, rec)] = reinterpret_cast<int64_t>(src);
+  }
+  __syncthreads();
+  encode_cta(wd, sh, tid, [&](const EncodePlan& plan, bool& raw) -> uint8_t* {
+    int at = -1;
+    if (plan.codes) {
+      // Claim page bytes with a CAS, so that a record too large for what is
+      // left does not block the block's smaller records.
+      int32_t* fill = s.fill + (int64_t)layer * s.NB + block;
+      const int need = kDenseBytes + plan.var_len;
+      int seen = *reinterpret_cast<volatile int32_t*>(fill);
+      while ((int64_t)seen + need <= page_bytes) {
+        const int before = atomicCAS(fill, seen, seen + need);
+        if (before == seen) {
+          at = seen;
+          break;
+        }
+        seen = before;
+      }
+      if (at < 0) atomicAdd(&s.counters[FP_CTR_SPILLS], 1);
+    }
+    atomicAdd(&s.counters[FP_CTR_ENCODED], 1);
+    if (at >= 0) {
+      uint8_t* dst = arena + (int64_t)block * page_bytes + at;
+      s.rec_addr[idx] = reinterpret_cast<int64_t>(dst);
+      s.rec_len[idx] = plan.var_len;
+      raw = false;
+      return dst;
+    }
+    raw = true;
+    atomicAdd(&s.counters[FP_CTR_FALLBACKS], 1);
+    const int slot = v.overflow_take((uint32_t)(block * 2 * s.H + rec));
+    if (slot < 0) {
+      atomicAdd(&s.counters[FP_CTR_ERR_OVERFLOW], 1);
+      return nullptr;
+    }
+    uint8_t* dst = s.overflow + (int64_t)slot * kRawRecord;
+    s.rec_addr[idx] = reinterpret_cast<int64_t>(dst);
+    s.rec_len[idx] = kRawVarLen;
+    return dst;
+  });
+}
+
+// Loads a token-major [128,128] BF16 tile (row stride `row_bytes`) into the
+// swizzled shared tile with coalesced 16-byte accesses.
+__device__ __forceinline__ void tile_load(uint8_t* tile, const uint8_t* src, int64_t row_bytes,
+                                          int tid) {
+#pragma unroll
+  for (int q = 0; q < 8; ++q) {
+    const int x = q * kOwners + tid, r = x >> 4, ch = x & 15;
+    *reinterpret_cast<uint4*>(tile + r * 256 + (((ch ^ r) & 15) << 4)) =
+        *reinterpret_cast<const uint4*>(src + r * row_bytes + ch * 16);
+  }
+}
+
+__device__ __forceinline__ void tile_store(const uint8_t* tile, uint8_t* dst, int64_t row_bytes,
+                                           int tid) {
+#pragma unroll
+  for (int q = 0; q < 8; ++q) {
+    const int x = q * kOwners + tid, r = x >> 4, ch = x & 15;
+    *reinterpret_cast<uint4*>(dst + r * row_bytes + ch * 16) =
+        *reinterpret_cast<const uint4*>(tile + r * 256 + (((ch ^ r) & 15) << 4));
+  }
+}
+
+// Fragment words of owner `tid` out of a token-major shared tile.
+__device__ __forceinline__ void tile_to_words(uint8_t* tile, int kv, int tid, uint4 (&wd)[8]) {
+  const OwnerCoords o(tid);
+#pragma unroll
+  for (int st = 0; st < 8; ++st) {
+    uint32_t w[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int j = i >> 1, f = i & 1;
+      if (kv == 0) {
+        w[i] = *reinterpret_cast<const uint32_t*>(tile_at(tile, o.row(j), o.col(st, f)));
+      } else {
+        const int tok = o.col(st, f), dim = o.row(j);
+        w[i] = (uint32_t)*reinterpret_cast<const uint16_t*>(tile_at(tile, tok, dim)) |
+               ((uint32_t)*reinterpret_cast<const uint16_t*>(tile_at(tile, tok + 1, dim)) << 16);
+      }
+    }
+    wd[st] = make_uint4(w[0], w[1], w[2], w[3]);
+  }
+}
+
+__device__ __forceinline__ void word_to_tile(uint8_t* tile, int kv, const OwnerCoords& o, int st,
+                                             const uint32_t (&w)[4]) {
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int j = i >> 1, f = i & 1;
+    if (kv == 0) {
+      *reinterpret_cast<uint32_t*>(tile_at(tile, o.row(j), o.col(st, f))) = w[i];
+    } else {
+      const int tok = o.col(st, f), dim = o.row(j);
+      *reinterpret_cast<uint16_t*>(tile_at(tile, tok, dim)) = (uint16_t)w[i];
+      *reinterpret_cast<uint16_t*>(tile_at(tile, tok + 1, dim)) = (uint16_t)(w[i] >> 16);
+    }
+  }
+}
+
+constexpr int kTileBytes = 128 * 256;
+
+// Batch encoder over token-major records: grid = records.
+__global__ void __launch_bounds__(kOwners)
+encode_records_kernel(const uint8_t* raw, const uint8_t* rank_of, const int32_t* table_index,
+                      const int32_t* kv, uint8_t* out, int64_t out_stride, int32_t* out_len) {
+  extern __shared__ __align__(16) uint8_t dyn[];
+  uint8_t* tile = dyn;
+  EncodeShared& sh = *reinterpret_cast<EncodeShared*>(dyn + kTileBytes);
+  const int64_t i = blockIdx.x;
+  const int tid = threadIdx.x;
+  const int which = kv[i];
+  sh.rank[tid] = rank_of[(int64_t)(table_index ? table_index[i] : (int32_t)i) * 256 + tid];
+  tile_load(tile, raw + i * kRawRecord, 256, tid);
+  __syncthreads();
+  uint4 wd[8];
+  tile_to_words(tile, which, tid, wd);
+  uint8_t* dst = out + i * out_stride;
+  encode_cta(wd, sh, tid, [&](const EncodePlan& plan, bool& raw_out) -> uint8_t* {
+    raw_out = !plan.codes;
+    out_len[i] = plan.codes ? kDenseBytes + plan.var_len : kRawRecord;
+    return dst;
+  });
+}
+
+// One record -> token-major rows of `row_bytes` stride starting at `dst`.
+__device__ __forceinline__ void decode_to_rows(const uint8_t* rec, int vlen, const HeadTables& tab,
+                                               int kv, uint8_t* tile, uint8_t* esc, uint8_t* dst,
+                                               int64_t row_bytes, int tid) {
+  const OwnerCoords o(tid);
+  auto emit = [&](int st, const uint32_t (&w)[4]) { word_to_tile(tile, kv, o, st, w); };
+  if (vlen > kVarCap)
+    raw_record_words(rec, tid, emit);
+  else
+    coded_record_words(rec, tab, esc, tid, [] {}, emit);
+  __syncthreads();
+  tile_store(tile, dst, row_bytes, tid);
+}
+
+constexpr int kDecodeSmem = kTileBytes + kEscBytes;
+
+// Prefill decompressor: grid (pages, 2 H).  hbm_kv.cu:452-494.
+__global__ void __launch_bounds__(kOwners)
+gather_kernel(const int32_t* blocks, const int64_t* rec_addr, const int32_t* rec_len,
+              const int32_t* plut, const uint8_t* slut, uint8_t* wk, uint8_t* wv, int H) {
+  extern __shared__ __align__(16) uint8_t dyn[];
+  const int rec = blockIdx.y, kv = rec / H, head = rec % H;
+  const int64_t idx = (int64_t)blocks[blockIdx.x] * 2 * H + rec;
+  const HeadTables tab = load_tables(plut, slut, rec);
+  uint8_t* dst = (kv == 0 ? wk : wv) + ((int64_t)blockIdx.x * 128 * H + head) * 256;
+  decode_to_rows(reinterpret_cast<const uint8_t*>(rec_addr[idx]), rec_len[idx], tab, kv, dyn,
+                 dyn + kTileBytes, dst, (int64_t)H * 256, threadIdx.x);
+}
+
+// Batch decoder: grid = records.
+__global__ void __launch_bounds__(kOwners)
+decode_records_kernel(const uint8_t* recs, int64_t rec_stride, const int32_t* rec_len,
+                      const int32_t* plut, const uint8_t* slut, const int32_t* table_index,
+                      const int32_t* kv, uint8_t* out) {
+  extern __shared__ __align__(16) uint8_t dyn[];
+  const int64_t i = blockIdx.x;
+  const HeadTables tab = load_tables(plut, slut, table_index ? table_index[i] : (int32_t)i);
+  decode_to_rows(recs + i * rec_stride, rec_len[i], tab, kv[i], dyn, dyn + kTileBytes,
+                 out + i * kRawRecord, 256, threadIdx.x);
+}
+
+int check_store(const fp_store* st) {
+  FP_REQUIRE(st != nullptr, "store is null");
+  FP_REQUIRE(st->counters && st->wslot && st->tags && st->free_stack && st->ovf_bits &&
+                 st->claim_list && st->close_list && st->rec_addr && st->rec_len && st->fill,
+             "store has a null table");
+  FP_REQUIRE(st->L > 0 && st->H > 0 && st->NB > 0 && st->cap >= 0, "bad store geometry");
+  return FP_OK;
+}
+
+template <typename Kernel>
+int allow_smem(Kernel kernel, int bytes) {
+  return cuda_status(
+      cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes),
+      "cudaFuncSetAttribute");
+}
+
+}  // namespace
+}  // namespace fpb
+
+using namespace fpb;
+
+extern "C" {
+
+const char* fp_last_error(void) { return last_error(); }
+
+const char* fp_version(void) { return "fragpack_b200 0.1.0 (sm_100a)"; }
+
+int fp_hbm_prepare(const fp_store* store, const int64_t* slot_mapping, int64_t num_tokens,
+                   const int32_t* live, int64_t num_live, int32_t step, void* stream) {
+  if (int rc = check_store(store)) return rc;
+  FP_REQUIRE(num_tokens >= 0 && num_tokens <= store->cap, "block lists too small for %lld tokens",
+             (long long)num_tokens);
+  FP_REQUIRE(num_tokens == 0 || slot_mapping, "slot_mapping is null");
+  FP_REQUIRE(num_live >= 0 && (num_live == 0 || live), "live list is null");
+  StoreView v{*store};
+  prepare_kernel<<<1, kPrepareThreads, 0, (cudaStream_t)stream>>>(
+      v, slot_mapping, (int)num_tokens, live, (int)num_live, step);
+  FP_LAUNCH_CHECK("prepare_kernel");
+  return FP_OK;
+}
+
+int fp_hbm_write(const fp_store* store, const void* key, int64_t k_stride0, int64_t k_stride1,
+                 const void* value, int64_t v_stride0, int64_t v_stride1,
+                 const int64_t* slot_mapping, int64_t num_tokens, int32_t layer, void* stream) {
+  if (int rc = check_store(store)) return rc;
+  if (num_tokens == 0) return FP_OK;
+  FP_REQUIRE(key && value && slot_mapping, "null key / value / slot_mapping");
+  FP_REQUIRE(layer >= 0 && layer < store->L, "layer %d out of range", layer);
+  FP_REQUIRE((reinterpret_cast<uintptr_t>(key) | reinterpret_cast<uintptr_t>(value)) % 4 == 0 &&
+                 (k_stride0 | k_stride1 | v_stride0 | v_stride1) % 2 == 0,
+             "key / value rows must be 4-byte aligned");
+  StoreView v{*store};
+  write_kernel<<<(unsigned)num_tokens, 256, 0, (cudaStream_t)stream>>>(
+      v, static_cast<const uint16_t*>(key), static_cast<const uint16_t*>(value), k_stride0,
+      k_stride1, v_stride0, v_stride1, slot_mapping, layer);
+  FP_LAUNCH_CHECK("write_kernel");
+  return FP_OK;
+}
+
+int fp_hbm_encode(const fp_store* store, const uint8_t* rank_of, int32_t layer, uint8_t* arena,
+                  int64_t page_bytes, int64_t max_close, void* stream) {
+  if (int rc = check_store(store)) return rc;
+  if (max_close == 0) return FP_OK;
+  FP_REQUIRE(max_close > 0 && max_close <= store->cap, "close list too small");
+  FP_REQUIRE(rank_of && arena, "null rank_of / arena");
+  FP_REQUIRE(layer >= 0 && layer < store->L, "layer %d out of range", layer);
+  FP_REQUIRE(page_bytes % 16 == 0 && page_bytes > 0 && page_bytes < (1LL << 31),
+             "bad arena page size %lld", (long long)page_bytes);
+  FP_REQUIRE(reinterpret_cast<uintptr_t>(arena) % 16 == 0, "arena must be 16-byte aligned");
+  StoreView v{*store};
+  encode_kernel<<<dim3((unsigned)max_close, 2 * store->H), kOwners, 0, (cudaStream_t)stream>>>(
+      v, layer, arena, page_bytes, rank_of);
+  FP_LAUNCH_CHECK("encode_kernel");
+  return FP_OK;
+}
+
+int fp_hbm_commit(const fp_store* store, void* stream) {
+  if (int rc = check_store(store)) return rc;
+  StoreView v{*store};
+  commit_kernel<<<1, 256, 0, (cudaStream_t)stream>>>(v);
+  FP_LAUNCH_CHECK("commit_kernel");
+  return FP_OK;
+}
+
+int fp_hbm_gather(const int32_t* blocks, int64_t n, const int64_t* rec_addr,
+                  const int32_t* rec_len, const int32_t* plut, const uint8_t* slut, void* wk,
+                  void* wv, int64_t workspace_bytes, int32_t kv_heads, void* stream) {
+  if (n == 0) return FP_OK;
+  FP_REQUIRE(n > 0 && blocks && rec_addr && rec_len && plut && slut && wk && wv,
+             "null gather argument");
+  FP_REQUIRE(kv_heads > 0 && 2 * kv_heads <= 65535, "bad kv_heads %d", kv_heads);
+  FP_REQUIRE(workspace_bytes >= n * 128 * (int64_t)kv_heads * 256, "workspace too small");
+  FP_REQUIRE((reinterpret_cast<uintptr_t>(wk) | reinterpret_cast<uintptr_t>(wv)) % 16 == 0,
+             "workspace must be 16-byte aligned");
+  static int allowed = allow_smem(gather_kernel, kDecodeSmem);
+  if (allowed) return allowed;
+  gather_kernel<<<dim3((unsigned)n, 2 * kv_heads), kOwners, kDecodeSmem, (cudaStream_t)stream>>>(
+      blocks, rec_addr, rec_len, plut, slut, static_cast<uint8_t*>(wk), static_cast<uint8_t*>(wv),
+      kv_heads);
+  FP_LAUNCH_CHECK("gather_kernel");
+  return FP_OK;
+}
+
+int fp_encode_records(const void* raw, int64_t n, const uint8_t* rank_of,
+                      const int32_t* table_index, const int32_t* kv, uint8_t* out,
+                      int64_t out_stride, int32_t* out_len, void* stream) {
+  if (n == 0) return FP_OK;
+  FP_REQUIRE(n > 0 && n < (1LL << 31) && raw && rank_of && kv && out && out_len,
+             "null encode argument");
+  FP_REQUIRE(out_stride >= kRawRecord && out_stride % 16 == 0, "bad out_stride %lld",
+             (long long)out_stride);
+  FP_REQUIRE((reinterpret_cast<uintptr_t>(raw) | reinterpret_cast<uintptr_t>(out)) % 16 == 0,
+             "buffers must be 16-byte aligned");
+  constexpr int smem = kTileBytes + (int)sizeof(EncodeShared);
+  static int allowed = allow_smem(encode_records_kernel, smem);
+  if (allowed) return allowed;
+  encode_records_kernel<<<(unsigned)n, kOwners, smem, (cudaStream_t)stream>>>(
+      static_cast<const uint8_t*>(raw), rank_of, table_index, kv, out, out_stride, out_len);
+  FP_LAUNCH_CHECK("encode_records_kernel");
+  return FP_OK;
+}
+
+int fp_decode_records(const uint8_t* recs, int64_t rec_stride, const int32_t* rec_len, int64_t n,
+                      const int32_t* plut, const uint8_t* slut, const int32_t* table_index,
+                      const int32_t* kv, void* out, void* stream) {
+  if (n == 0) return FP_OK;
+  FP_REQUIRE(n > 0 && n < (1LL << 31) && recs && rec_len && plut && slut && kv && out,
+             "null decode argument");
+  FP_REQUIRE(rec_stride % 16 == 0 && rec_stride >= kDenseBytes + kHeaderBytes,
+             "bad rec_stride %lld", (long long)rec_stride);
+  FP_REQUIRE((reinterpret_cast<uintptr_t>(recs) | reinterpret_cast<uintptr_t>(out)) % 16 == 0,
+             "buffers must be 16-byte aligned");
+  static int allowed = allow_smem(decode_records_kernel, kDecodeSmem);
+  if (allowed) return allowed;
+  decode_records_kernel<<<(unsigned)n, kOwners, kDecodeSmem, (cudaStream_t)stream>>>(
+      recs, rec_stride, rec_len, plut, slut, table_index, kv, static_cast<uint8_t*>(out));
+  FP_LAUNCH_CHECK("decode_records_kernel");
+  return FP_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,184 @@
+/*
+ * fragpack_b200 - C ABI of the B200 (sm_100a) FragPack hot path.
+ *
+ * Every entry point takes plain device pointers, sizes and a CUDA stream
+ * (passed as void*, a cudaStream_t), enqueues its kernels on that stream
+ * without synchronising, and returns 0 or a negative FP_ERR_* code;
+ * fp_last_error() then describes the failure.  Nothing here allocates device
+ * memory.  Each function replaces one function of the reference's pybind11
+ * module `fragpack_cuda` (fragpack/ops/fragpack_ext.cpp:57-66); the reference
+ * file:line of the replaced function is given with each declaration.
+ *
+ * Layouts (identical to the reference):
+ *   record      see fragpack/compression/attn_page.py:1-44
+ *   rec_addr    int64 [L, NB, 2, H]  absolute device address of each record
+ *   rec_len     int32 [L, NB, 2, H]  record bytes - 22528; 10240 marks a raw record
+ *   plut        int32 [.., 2, H, 2]  primary prmt words      (attn_tables.py:96-124)
+ *   slut        uint8 [.., 2, H, 16] extended table
+ *   rank_of     uint8 [L, 2, H, 256] table rank of a high byte, 255 = absent
+ */
+#ifndef FRAGPACK_B200_H_
+#define FRAGPACK_B200_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define FP_OK 0
+#define FP_ERR_ARGUMENT (-1) /* rejected arguments; nothing was enqueued */
+#define FP_ERR_CUDA (-2)     /* a CUDA runtime call or launch failed */
+
+/* Counter slots of fp_store.counters (fragpack/ops/hbm_kv.cu:14-26). */
+enum {
+  FP_CTR_FREE_TOP = 0,
+  FP_CTR_TRANSIENT = 1,
+  FP_CTR_CLAIMS = 2,
+  FP_CTR_CLOSES = 3,
+  FP_CTR_ERR_STAGING = 4,
+  FP_CTR_ERR_OVERFLOW = 5,
+  FP_CTR_FALLBACKS = 6,
+  FP_CTR_ENCODED = 7,
+  FP_CTR_SPILLS = 8,
+  FP_CTR_HEIRS = 9,
+  FP_CTR_DONORS = 10,
+  FP_NUM_COUNTERS = 16
+};
+
+/* Import status bits (fragpack/ops/hbm_kv.cu:507). */
+enum { FP_BLOB_BAD_HEADER = 1, FP_BLOB_BAD_LENGTHS = 2, FP_BLOB_NO_OVERFLOW = 4 };
+
+/* Bits of the decode status word (see fp_fused_decode). */
+enum { FP_DECODE_WAIT_TIMEOUT = 1 };
+
+/*
+ * The store state that the reference passes as 13 positional tensors to every
+ * hbm_* function (fragpack/ops/hbm_kv.py:287-301, hbm_kv.cu:32-78).
+ */
+typedef struct fp_store {
+  int32_t* counters;    /* [FP_NUM_COUNTERS] */
+  int32_t* wslot;       /* [NB] staging slot of an open block, -1 if none */
+  int32_t* tags;        /* [4, NB] per-block step stamps */
+  int32_t* free_stack;  /* [S_p] */
+  uint32_t* ovf_bits;   /* [ovf_words] overflow slots in use (tail bits preset) */
+  int32_t* claim_list;  /* [2, cap] claimed blocks, then heirs */
+  int32_t* close_list;  /* [2, cap] closing blocks, then the heir of each */
+  int64_t* rec_addr;    /* [L, NB, 2, H] */
+  int32_t* rec_len;     /* [L, NB, 2, H] */
+  uint8_t* staging;     /* [S_p, L, 2, H, 32768] persistent staging */
+  uint8_t* scratch;     /* [S_t, 2, H, 32768] one layer of transient staging */
+  uint8_t* overflow;    /* [O, 32768] raw records that do not code or fit */
+  int32_t* fill;        /* [L, NB] bytes used in each block-layer page */
+  int64_t overflow_records; /* O */
+  int32_t L, H, NB, S_p, S_t, ovf_words, cap;
+} fp_store;
+
+/* Message of the calling thread's last failed call ("" if none). */
+const char* fp_last_error(void);
+
+/* Library version string. */
+const char* fp_version(void);
+
+/*
+ * Element counts of the decode workspace for `kv_heads` and `units`
+ * (replaces fragpack/ops/fused_attn_decode.py:88-102 workspace_elems):
+ * float elements of `opart` and `ml`, int32 elements of `plan`.
+ */
+int fp_decode_workspace(int32_t kv_heads, int32_t units, int64_t* opart_elems, int64_t* ml_elems,
+                        int64_t* plan_elems);
+
+/*
+ * Split-KV decode attention for one query token per sequence over compressed
+ * KV records.  Replaces fused_decode (fragpack/ops/fused_attn_decode.cu:429-478,
+ * bound at fragpack_ext.cpp:60), with the query group handled natively.
+ *
+ *   q, out       BF16 [B, H * group, 128]; row strides in elements, head stride 128
+ *   rec_addr/rec_len  one layer: [NB, 2, H]
+ *   plut/slut    one layer: [2, H, 2] / [2, H, 16]
+ *   block_table  int32 [B, >= pages]; row stride in elements
+ *   seq_lens     int32 [B]; 0 gives a zero output row
+ *   opart/ml/plan workspace sized by fp_decode_workspace
+ *   group        query heads per KV head: 1, 2, 4 or 8
+ *   units        work-unit capacity per KV head, >= B
+ *   replan       nonzero: recompute the plan from seq_lens (first layer of a step)
+ * The last int32 of `plan` is a status word: the kernels OR FP_DECODE_* bits
+ * into it when a bounded device-side wait ran out (results are then invalid).
+ */
+int fp_fused_decode(const void* q, int64_t q_stride, const int64_t* rec_addr,
+                    const int32_t* rec_len, const int32_t* plut, const uint8_t* slut,
+                    const int32_t* block_table, int64_t bt_stride, const int32_t* seq_lens,
+                    float* opart, int64_t opart_elems, float* ml, int64_t ml_elems, int32_t* plan,
+                    int64_t plan_elems, void* out, int64_t out_stride, int32_t batch,
+                    int32_t kv_heads, int32_t group, int32_t units, int32_t replan, float scale,
+                    int32_t num_sms, void* stream);
+
+/* hbm_prepare (fragpack/ops/hbm_kv.cu:669-686): start a step. */
+int fp_hbm_prepare(const fp_store* store, const int64_t* slot_mapping, int64_t num_tokens,
+                   const int32_t* live, int64_t num_live, int32_t step, void* stream);
+
+/*
+ * hbm_write (fragpack/ops/hbm_kv.cu:688-705): scatter new K / V tokens
+ * BF16 [N, H, 128] (strides in elements, head dim contiguous) into staging.
+ */
+int fp_hbm_write(const fp_store* store, const void* key, int64_t k_stride0, int64_t k_stride1,
+                 const void* value, int64_t v_stride0, int64_t v_stride1,
+                 const int64_t* slot_mapping, int64_t num_tokens, int32_t layer, void* stream);
+
+/*
+ * hbm_encode (fragpack/ops/hbm_kv.cu:707-723): the block encoder.  Codes this
+ * layer's records of every block closed this step into the block's arena page
+ * (`arena` + block * `page_bytes`) or raw into the overflow pool.  Output
+ * bytes equal attn_page.encode_record (attn_page.py:146-209).
+ */
+int fp_hbm_encode(const fp_store* store, const uint8_t* rank_of, int32_t layer, uint8_t* arena,
+                  int64_t page_bytes, int64_t max_close, void* stream);
+
+/* hbm_commit (fragpack/ops/hbm_kv.cu:725-734): release closed blocks' staging. */
+int fp_hbm_commit(const fp_store* store, void* stream);
+
+/*
+ * hbm_gather (fragpack/ops/hbm_kv.cu:736-753): the prefill decompressor.
+ * Decodes records of `blocks[i]` of one layer into token-major BF16 pages
+ * wk / wv [>= n, 128, H, 128].
+ */
+int fp_hbm_gather(const int32_t* blocks, int64_t n, const int64_t* rec_addr,
+                  const int32_t* rec_len, const int32_t* plut, const uint8_t* slut, void* wk,
+                  void* wv, int64_t workspace_bytes, int32_t kv_heads, void* stream);
+
+/* hbm_export (fragpack/ops/hbm_kv.cu:755-774): closed blocks -> block blobs. */
+int fp_hbm_export(const int32_t* blocks, int64_t n, const int64_t* rec_addr,
+                  const int32_t* rec_len, uint8_t* out, int64_t out_bytes, int64_t stride,
+                  int64_t* lengths, int32_t L, int32_t H, int32_t NB, int64_t digest, void* stream);
+
+/* hbm_import (fragpack/ops/hbm_kv.cu:776-802): block blobs -> blocks of this store. */
+int fp_hbm_import(const fp_store* store, const uint8_t* src, int64_t src_bytes,
+                  const int64_t* offsets, const int32_t* blocks, int64_t n, int32_t* status,
+                  const int64_t* arena_base, const int64_t* arena_stride, int64_t digest,
+                  void* stream);
+
+/*
+ * Batch form of attn_page.encode_record (fragpack/compression/attn_page.py:146-209)
+ * on the device: record i is token-major uint16 [128,128] at raw + i * 32768,
+ * coded with table `rank_of + 256 * table_index[i]` as K (kv[i] = 0) or V (1)
+ * into out + i * out_stride (>= 32768, 16-byte multiple); out_len[i] receives
+ * the record bytes (32768 for the raw fallback).
+ */
+int fp_encode_records(const void* raw, int64_t n, const uint8_t* rank_of,
+                      const int32_t* table_index, const int32_t* kv, uint8_t* out,
+                      int64_t out_stride, int32_t* out_len, void* stream);
+
+/*
+ * Batch form of attn_page.decode_record (attn_page.py:212-269): record i at
+ * recs + i * rec_stride with rec_len[i] bytes past the dense part (10240 =
+ * raw) is decoded to token-major uint16 [128,128] at out + i * 32768.
+ */
+int fp_decode_records(const uint8_t* recs, int64_t rec_stride, const int32_t* rec_len, int64_t n,
+                      const int32_t* plut, const uint8_t* slut, const int32_t* table_index,
+                      const int32_t* kv, void* out, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* FRAGPACK_B200_H_ */
