@@ -1,0 +1,573 @@
+"""Headline benchmark: decode attention over HBM-resident compressed KV.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+                    [--workload c2|c3|c5] [--layers R] [--no-graph]
+
+A "step" is one decode step of the workload: the plan is computed once, then
+every resident layer runs fused decode attention (one query token per
+sequence).  With N = 1 the workload is the Qwen3-30B-A3B-like configuration
+(48 layers, 4 KV heads, GQA 8, batch 4 at context 8192); with N > 1 it is the
+Llama-3-70B-like configuration (8 KV heads, GQA 8, batch 128 at context 32768)
+sharded by KV head, one process per GPU, with the per-head outputs all-gathered
+over NCCL into the o_proj input layout after every layer.
+
+Rank 0 prints ONE JSON line.  ``value`` is the effective logical-KV bandwidth
+(BF16 bytes of the KV attended per second, whole job), measured with the KV
+resident in HBM; ``e2e`` is the same metric through the public API with host
+buffers (queries, lengths and block tables copied in, outputs copied out, per
+step); ``roofline`` rates the decode kernel on COMPRESSED bytes against the
+measured HBM copy bandwidth; ``cpu_baseline`` times the CPU oracle codec plus
+torch CPU fp32 attention on a bounded sample of the same workload.
+
+``--impl reference`` runs that CPU pipeline alone (all host threads) as the
+reference arm.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+from pathlib import Path
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+import torch
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+from fragpack_b200 import workloads  # noqa: E402
+from fragpack_b200.compression import attn_page as ap  # noqa: E402
+
+METRIC = "decode_attn_effective_logical_kv_bandwidth"
+UNIT = "TB/s"
+SCALE = 128**-0.5
+L2_BYTES = 126 * 2**20
+FALLBACK_HBM_GBS = 6650.0
+
+
+def measured_hbm_peak() -> tuple[float, str]:
+    path = ROOT / "MEASURED_PEAKS.json"
+    if path.exists():
+        try:
+            return float(json.loads(path.read_text())["hbm_gbs"]), "measured"
+        except (KeyError, ValueError):
+            pass
+    return FALLBACK_HBM_GBS, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while a region runs."""
+
+    FIELDS = (
+        "clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
+        "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+        "clocks_event_reasons.sw_power_cap"
+    )
+
+    def __init__(self, index: int) -> None:
+        self.index = index
+        self.rows: list[list[str]] = []
+        self._stop = threading.Event()
+        self._thread = threading.Thread(target=self._run, daemon=True)
+
+    def _run(self) -> None:
+        while not self._stop.is_set():
+            try:
+                out = subprocess.run(
+                    ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                     "-i", str(self.index)],
+                    capture_output=True, text=True, timeout=5,
+                ).stdout.strip()
+                if out:
+                    self.rows.append([c.strip() for c in out.split(",")])
+            except (OSError, subprocess.SubprocessError):
+                return
+            self._stop.wait(0.1)
+
+    def __enter__(self) -> "ClockSampler":
+        self._thread.start()
+        return self
+
+    def __exit__(self, *exc) -> None:
+        self._stop.set()
+        self._thread.join(timeout=10)
+
+    def summary(self) -> dict:
+        sm, mx, reasons = [], [], set()
+        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+        for row in self.rows:
+            try:
+                sm.append(float(row[0]))
+                mx.append(float(row[1]))
+            except (ValueError, IndexError):
+                continue
+            for name, cell in zip(names, row[2:6]):
+                if cell.lower().startswith("active"):
+                    reasons.add(name)
+        return {
+            "sm_mhz": float(np.median(sm)) if sm else None,
+            "sm_max_mhz": max(mx) if mx else None,
+            "reasons": sorted(reasons),
+            "samples": len(sm),
+        }
+
+
+# --------------------------------------------------------------------------
+# CPU pipeline (oracle codec + torch fp32 attention): baseline and reference arm
+# --------------------------------------------------------------------------
+def cpu_pipeline(sample: dict, repeats: int = 1) -> tuple[float, float, int]:
+    """Decode the sample's records on the host cores and attend over them.
+
+    Args:
+        sample: ``records u8[n,32768]``, ``lens i32[n]``, ``tables u8[n,22]``,
+            ``kv i32[n]``, ``q`` float32 ``[n_seq_heads, G, 128]``, ``pages``
+            per (sequence, head) record ranges, ``seq_lens``.
+
+    Returns:
+        ``(seconds, logical_bytes, threads)`` for one pass.
+    """
+    import oracle
+
+    t0 = time.perf_counter()
+    for _ in range(repeats):
+        dec = oracle.decode_records(sample["records"], sample["lens"], sample["tables"], sample["kv"])
+        f32 = torch.from_numpy(oracle.bf16_bits_to_f32(dec))  # [n,128,128]
+        for (k0, k1, v0, v1, tokens), q in zip(sample["ranges"], sample["q"]):
+            k = f32[k0:k1].reshape(-1, 128)[:tokens]
+            v = f32[v0:v1].reshape(-1, 128)[:tokens]
+            oracle.attention_fp32(q, k, v, SCALE)
+    seconds = (time.perf_counter() - t0) / repeats
+    return seconds, float(sample["logical_bytes"]), oracle.threads()
+
+
+def sample_for_cpu(work: workloads.DecodeWorkload, layers: int, seqs: int) -> dict:
+    """Copy the records of ``layers`` x ``seqs`` sequences to the host (all heads)."""
+    store, cfg = work.store, work.cfg
+    heads = cfg.kv_heads
+    records, lens, tables, kvs, ranges, qs = [], [], [], [], [], []
+    bt = work.block_table.cpu().numpy()
+    rec_addr = store.rec_addr.cpu().numpy()
+    rec_len = store.rec_len.cpu().numpy()
+    gen = torch.Generator().manual_seed(7)
+    logical = 0
+    at = 0
+
+    pools = [(t.data_ptr(), t.numel(), t.view(-1)) for t in
+             (*work.arenas, store.staging, store.scratch, store.overflow, store.null_record)]
+
+    def fetch(addr: int, n: int) -> np.ndarray:
+        # A record lives in an arena page, in staging, in the overflow pool or
+        # is the shared null record: find the pool that holds its address.
+        for base, size, flat in pools:
+            if base <= addr < base + size:
+                out = np.zeros(32768, np.uint8)
+                out[:n] = flat[addr - base : addr - base + n].cpu().numpy()
+                return out
+        raise RuntimeError("record address outside every pool")
+
+    for layer in range(layers):
+        for b in range(seqs):
+            tokens = int(work.lens_host[b])
+            pages = (tokens + 127) // 128
+            for h in range(heads):
+                span = []
+                for kv in range(2):
+                    first = at
+                    for pg in range(pages):
+                        blk = bt[b, pg]
+                        n = int(rec_len[layer, blk, kv, h]) + ap.DENSE_BYTES
+                        records.append(fetch(int(rec_addr[layer, blk, kv, h]), n))
+                        lens.append(n)
+                        tables.append(work.table[layer, kv, h])
+                        kvs.append(kv)
+                        at += 1
+                    span += [first, at]
+                ranges.append((span[0], span[1], span[2], span[3], tokens))
+                qs.append(torch.randn(cfg.group, 128, generator=gen))
+                logical += tokens * 2 * 128 * 2
+    return {
+        "records": np.stack(records),
+        "lens": np.array(lens, np.int32),
+        "tables": np.stack(tables),
+        "kv": np.array(kvs, np.int32),
+        "ranges": ranges,
+        "q": qs,
+        "logical_bytes": logical,
+        "what": f"{layers} layer(s) x {seqs} sequence(s) x {heads} KV heads of {cfg.name}",
+    }
+
+
+# --------------------------------------------------------------------------
+# GPU arm
+# --------------------------------------------------------------------------
+def validate(work, queries, outputs, layer: int) -> tuple[float, float]:
+    """Max / mean abs error of ``outputs[layer]`` vs fp32 attention over the kept source KV."""
+    cfg = work.cfg
+    worst, total, count = 0.0, 0.0, 0
+    for (lay, b), kv in work.sample.items():
+        if lay != layer:
+            continue
+        k = kv[0].float()  # [T, H, 128]
+        v = kv[1].float()
+        for h in range(cfg.kv_heads):
+            q = queries[layer][b, h * cfg.group : (h + 1) * cfg.group].float()
+            ref = torch.softmax(q @ k[:, h].T * SCALE, -1) @ v[:, h]
+            err = (outputs[layer][b, h * cfg.group : (h + 1) * cfg.group].float() - ref).abs()
+            # The bar is absolute for outputs up to magnitude 1 and relative above
+            # it: BF16 outputs near 100 (x64 heavy-tail V) are spaced 0.5 apart.
+            err = err / ref.abs().clamp(min=1.0)
+            worst = max(worst, float(err.max()))
+            total += float(err.sum())
+            count += err.numel()
+    return worst, total / max(count, 1)
+
+
+def run_ours(args) -> dict:
+    from fragpack_b200.ops.fused_attn_decode import (
+        RecordTables,
+        decode_attention,
+        decode_status,
+        decode_units,
+        workspace_elems,
+    )
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    device = torch.device("cuda", local)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist_mod
+
+        dist = dist_mod
+        dist.init_process_group("nccl", device_id=device)
+
+    name = args.workload or ("c2" if world == 1 else "c5")
+    cfg = workloads.CONFIGS[name]
+    if args.batch or args.ctx:
+        # Reduced copies of a configuration, for profiler captures.
+        from dataclasses import replace
+
+        ctx = args.ctx or cfg.ctx_max
+        cfg = replace(cfg, name=f"{cfg.name}-reduced", batch=args.batch or cfg.batch,
+                      ctx_min=min(cfg.ctx_min, ctx), ctx_max=ctx)
+    if cfg.kv_heads % world:
+        raise SystemExit(f"{world} GPUs do not divide {cfg.kv_heads} KV heads")
+    per = cfg.kv_heads // world
+    head_slice = slice(rank * per, (rank + 1) * per)
+    # Resident layers: all of them when they fit, else as many as the budget holds.
+    per_layer = cfg.batch * ((cfg.ctx_max + 127) // 128) * 2 * per * (ap.DENSE_BYTES + 1280)
+    budget = int(args.hbm_budget_gb * 2**30)
+    layers = args.layers or max(1, min(cfg.layers, budget // max(per_layer, 1)))
+    work = workloads.build_decode_workload(
+        cfg, device, seed=args.seed, layers=layers, head_slice=head_slice,
+        keep_layers=(0, layers - 1),
+    )
+    cfg_built = work.cfg
+    B, H, G = cfg_built.batch, cfg_built.kv_heads, cfg_built.group
+    sms = torch.cuda.get_device_properties(device).multi_processor_count
+    units = decode_units(B, H, sms)
+    sizes = workspace_elems(H, units)
+    ws = (
+        torch.empty(sizes[0], device=device),
+        torch.empty(sizes[1], device=device),
+        torch.empty(sizes[2], dtype=torch.int32, device=device),
+    )
+    gen = torch.Generator(device=device).manual_seed(args.seed + 100 + rank)
+    queries = [
+        torch.randn(B, H * G, 128, generator=gen, device=device).to(torch.bfloat16)
+        for _ in range(layers)
+    ]
+    outputs = [torch.full_like(q, float("nan")) for q in queries]
+    tabs = [RecordTables(*work.store.layer_tables(layer)) for layer in range(layers)]
+    gathered = (
+        [torch.empty(world, B, H * G, 128, dtype=torch.bfloat16, device=device) for _ in range(layers)]
+        if world > 1 else None
+    )
+    oproj_in = (
+        [torch.empty(B, world * H * G, 128, dtype=torch.bfloat16, device=device) for _ in range(layers)]
+        if world > 1 else None
+    )
+
+    def attend(layer: int) -> None:
+        decode_attention(queries[layer], tabs[layer], work.block_table, work.seq_lens, SCALE,
+                         units, outputs[layer], ws, replan=layer == 0)
+
+    def step() -> None:
+        for layer in range(layers):
+            attend(layer)
+            if world > 1:
+                # Per-head outputs -> o_proj input layout [B, Hq, 128] on every rank.
+                dist.all_gather_into_tensor(gathered[layer], outputs[layer])
+                oproj_in[layer].view(B, world, H * G, 128).copy_(gathered[layer].transpose(0, 1))
+
+    # Correctness gate before any timing (outputs start as NaN).
+    step()
+    torch.cuda.synchronize()
+    if decode_status(ws, units):
+        raise SystemExit("decode kernel reported a timed-out wait")
+    worst = mean = 0.0
+    for layer in (0, layers - 1):
+        w, m = validate(work, queries, outputs, layer)
+        worst, mean = max(worst, w), max(mean, m)
+    if not (worst <= 1e-2 and mean <= 2e-3) or any(torch.isnan(o).any() for o in outputs):
+        raise SystemExit(f"validation failed: max-abs {worst:.3e}, mean-abs {mean:.3e}")
+
+    use_graph = not args.no_graph and world == 1
+    graph = None
+    if use_graph:
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            step()
+        torch.cuda.current_stream().wait_stream(side)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=side):
+            step()
+
+    def run_step() -> None:
+        if graph is not None:
+            graph.replay()
+        else:
+            step()
+
+    def barrier() -> None:
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(max(args.warmup, 3)):
+        run_step()
+    barrier()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with ClockSampler(local) as clocks:
+        start.record()
+        for _ in range(args.steps):
+            run_step()
+        stop.record()
+        barrier()
+    ms = start.elapsed_time(stop)
+    if dist is not None:
+        t = torch.tensor([ms], device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    ms_per_step = ms / args.steps
+
+    # Per-launch duration of the decode call of every layer, events on the
+    # launching stream (no graph), for the roofline of the dominant kernel.
+    per_call = []
+    for _ in range(3):
+        evs = [torch.cuda.Event(enable_timing=True) for _ in range(layers + 1)]
+        decode_attention(queries[0], tabs[0], work.block_table, work.seq_lens, SCALE, units,
+                         outputs[0], ws, replan=True)
+        evs[0].record()
+        for layer in range(layers):
+            decode_attention(queries[layer], tabs[layer], work.block_table, work.seq_lens, SCALE,
+                             units, outputs[layer], ws, replan=False)
+            evs[layer + 1].record()
+        torch.cuda.synchronize()
+        per_call.append(np.mean([evs[i].elapsed_time(evs[i + 1]) for i in range(layers)]))
+    call_ms = float(np.min(per_call))
+
+    # End to end through the public API with host buffers.
+    q_host = [q.cpu().pin_memory() for q in queries]
+    out_host = [torch.empty_like(q, device="cpu").pin_memory() for q in queries]
+    bt_host = work.block_table.cpu().pin_memory()
+    len_host = work.seq_lens.cpu().pin_memory()
+    h2d = sum(q.numel() * 2 for q in q_host) + bt_host.numel() * 4 + len_host.numel() * 4
+    d2h = sum(o.numel() * 2 for o in out_host)
+
+    def e2e_step() -> None:
+        work.block_table.copy_(bt_host, non_blocking=True)
+        work.seq_lens.copy_(len_host, non_blocking=True)
+        for layer in range(layers):
+            queries[layer].copy_(q_host[layer], non_blocking=True)
+        run_step()
+        for layer in range(layers):
+            out_host[layer].copy_(outputs[layer], non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+
+    for _ in range(3):
+        e2e_step()
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        e2e_step()
+    barrier()
+    e2e_ms = (time.perf_counter() - t0) * 1e3 / args.steps
+    if dist is not None:
+        t = torch.tensor([e2e_ms], device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_ms = float(t.item())
+
+    logical_all = work.logical_bytes * layers * world  # every rank holds an equal head shard
+    compressed_layer = float(np.mean(work.compressed_bytes))
+    peak, peak_kind = measured_hbm_peak()
+    achieved = compressed_layer / (call_ms * 1e-3) / 1e9
+    line = {
+        "metric": METRIC,
+        "value": logical_all / (ms_per_step * 1e-3) / 1e12,
+        "unit": UNIT,
+        "n_gpus": world,
+        "steps": args.steps,
+        "warmup": max(args.warmup, 3),
+        "ms_per_step": ms_per_step,
+        "higher_is_better": True,
+        "scaling": "strong" if world > 1 else "weak",
+        "vs_baseline": None,
+        "dtype": "bf16 KV and P, fp32 softmax/accumulate; u8/u32 integer decode",
+        "data": "synthetic (seeded per-channel lognormal-scaled Gaussian BF16 KV, K outlier channels)",
+        "config": {
+            "workload": cfg.name,
+            "layers_resident": layers,
+            "layers_model": cfg.layers,
+            "kv_heads_per_gpu": H,
+            "q_heads_per_gpu": H * G,
+            "batch": B,
+            "context": [int(work.lens_host.min()), int(work.lens_host.max())],
+            "parallelism": f"kv-head shard tp{world}" + (" + NCCL all-gather per layer" if world > 1 else ""),
+            "cuda_graph": bool(use_graph),
+            "l2_policy": "inputs larger than L2: every layer reads distinct pages, "
+                         f"{compressed_layer * layers / 2**20:.0f} MiB per step vs 126 MiB L2",
+        },
+        "us_per_layer": ms_per_step * 1e3 / layers,
+        "kv_ratio": work.logical_bytes / compressed_layer,
+        "compressed_gbs": compressed_layer * layers * world / (ms_per_step * 1e-3) / 1e9,
+        "e2e": {
+            "value": logical_all / (e2e_ms * 1e-3) / 1e12,
+            "unit": UNIT,
+            "h2d_bytes_per_step": h2d,
+            "d2h_bytes_per_step": d2h,
+            "ms_per_step": e2e_ms,
+        },
+        "gpu_launches": args.steps * (1 + 2 * layers),
+        "roofline": {
+            "bound": "hbm",
+            "kernel": "decode_attn_kernel (+ combine_kernel in the same call)",
+            "achieved": achieved,
+            "peak": peak,
+            "peak_kind": peak_kind,
+            "unit": "GB/s",
+            "frac": achieved / peak,
+            "traffic": None,
+            "algorithmic_bytes_per_launch": compressed_layer,
+            "launch_ms": call_ms,
+        },
+        "validation": {"max_abs": worst, "mean_abs": mean},
+        "clocks": clocks.summary(),
+    }
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        sample = sample_for_cpu(work, layers=min(layers, args.cpu_layers), seqs=min(B, args.cpu_seqs))
+        seconds, logical, threads = cpu_pipeline(sample)
+        line["cpu_baseline"] = {
+            "value": logical / seconds / 1e12,
+            "unit": UNIT,
+            "cores": threads,
+            "kind": "port",
+            "sample": sample["what"] + f" ({len(sample['lens'])} records, {seconds:.2f} s)",
+        }
+    if dist is not None:
+        dist.destroy_process_group()
+    return line if rank == 0 else {}
+
+
+def run_reference(args) -> dict:
+    """Reference arm: the CPU codec (oracle port) + torch CPU fp32 attention."""
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if rank != 0:
+        return {}
+    import oracle
+    from fragpack_b200 import synth
+
+    name = args.workload or ("c2" if world == 1 else "c5")
+    cfg = workloads.CONFIGS[name]
+    # Bounded sample of the workload: one layer, a few (sequence, head) pairs.
+    rng = np.random.default_rng(args.seed)
+    scales = synth.channel_scales(args.seed + 1, 1, cfg.kv_heads)[0]
+    tokens = min(cfg.ctx_max, 8192)
+    pairs = args.cpu_pairs
+    dump = synth.calibration_dump(args.seed + 4, scales[None], 16)
+    table = oracle.calibrate(dump)[0]
+    records, tables, kvs, ranges, qs = [], [], [], [], []
+    at = 0
+    pages = tokens // 128
+    for pair in range(pairs):
+        h = pair % cfg.kv_heads
+        kv = synth.kv_tokens_numpy(rng, scales[:, h : h + 1], tokens, cfg.heavy, cfg.junk)
+        span = []
+        for k in range(2):
+            first = at
+            for pg in range(pages):
+                records.append(kv[k, pg * 128 : (pg + 1) * 128, 0])
+                tables.append(table[k, h])
+                kvs.append(k)
+                at += 1
+            span += [first, at]
+        ranges.append((span[0], span[1], span[2], span[3], tokens))
+        qs.append(torch.randn(cfg.group, 128))
+    enc, lens = oracle.encode_records(np.stack(records), np.stack(tables), np.array(kvs, np.int32))
+    sample = {
+        "records": enc, "lens": lens, "tables": np.stack(tables), "kv": np.array(kvs, np.int32),
+        "ranges": ranges, "q": qs, "logical_bytes": pairs * tokens * 2 * 128 * 2,
+    }
+    for _ in range(max(args.warmup, 1)):
+        cpu_pipeline(sample)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        seconds, logical, threads = cpu_pipeline(sample)
+    ms = (time.perf_counter() - t0) * 1e3 / args.steps
+    value = logical / (ms * 1e-3) / 1e12
+    what = f"{pairs} (sequence, KV head) pairs x {tokens} tokens of one layer of {cfg.name} per step"
+    return {
+        "impl": "reference",
+        "metric": METRIC,
+        "value": value,
+        "unit": UNIT,
+        "n_gpus": world,
+        "steps": args.steps,
+        "warmup": max(args.warmup, 1),
+        "ms_per_step": ms,
+        "higher_is_better": True,
+        "scaling": "weak",
+        "vs_baseline": None,
+        "dtype": "u8/u16 integer decode, fp32 attention",
+        "data": "synthetic",
+        "config": {"workload": cfg.name, "sample": what},
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": threads, "kind": "port", "sample": what},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+
+
+def main() -> None:
+    parser = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawTextHelpFormatter)
+    parser.add_argument("--gpus", type=int, default=1)
+    parser.add_argument("--steps", type=int, default=20)
+    parser.add_argument("--warmup", type=int, default=5)
+    parser.add_argument("--impl", choices=("ours", "reference"), default="ours")
+    parser.add_argument("--workload", choices=("c2", "c3", "c5"), default=None)
+    parser.add_argument("--layers", type=int, default=0, help="resident layers (default: what fits)")
+    parser.add_argument("--hbm-budget-gb", type=float, default=40.0)
+    parser.add_argument("--seed", type=int, default=0)
+    parser.add_argument("--batch", type=int, default=0, help="override the batch (profiling)")
+    parser.add_argument("--ctx", type=int, default=0, help="override the context (profiling)")
+    parser.add_argument("--no-graph", action="store_true")
+    parser.add_argument("--no-cpu-baseline", action="store_true")
+    parser.add_argument("--cpu-layers", type=int, default=8)
+    parser.add_argument("--cpu-seqs", type=int, default=4)
+    parser.add_argument("--cpu-pairs", type=int, default=8)
+    args = parser.parse_args()
+    line = run_reference(args) if args.impl == "reference" else run_ours(args)
+    if line:
+        print(json.dumps(line))
+
+
+if __name__ == "__main__":
+    main()

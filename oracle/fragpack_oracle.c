@@ -16,6 +16,9 @@
 #include <stdint.h>
 #include <stdlib.h>
 #include <string.h>
+#ifdef _OPENMP
+#include <omp.h>
+#endif
 
 #define PAGE_TOKENS 128
 #define HEAD_DIM 128
@@ -282,4 +285,13 @@ void fpo_raw_record(const uint16_t* raw, int kv, uint8_t* out) {
       for (int i = 0; i < 8; ++i)
         put_u16(out + 16 * (256 * st + t) + 2 * i,
                 raw[kernel_pos_to_token_major(kv, 64 * t + 8 * st + i)]);
+}
+
+/* Host threads the batch forms use. */
+int fpo_threads(void) {
+#ifdef _OPENMP
+  return omp_get_max_threads();
+#else
+  return 1;
+#endif
 }
