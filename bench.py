@@ -316,7 +316,8 @@ def run_ours(args) -> dict:
     for layer in (0, layers - 1):
         w, m = validate(work, queries, outputs, layer)
         worst, mean = max(worst, w), max(mean, m)
-    if not (worst <= 1e-2 and mean <= 2e-3) or any(torch.isnan(o).any() for o in outputs):
+    failed = not (worst <= 1e-2 and mean <= 2e-3) or any(torch.isnan(o).any() for o in outputs)
+    if failed and not args.skip_validation:
         raise SystemExit(f"validation failed: max-abs {worst:.3e}, mean-abs {mean:.3e}")
 
     use_graph = not args.no_graph and world == 1
@@ -559,6 +560,8 @@ def main() -> None:
     parser.add_argument("--batch", type=int, default=0, help="override the batch (profiling)")
     parser.add_argument("--ctx", type=int, default=0, help="override the context (profiling)")
     parser.add_argument("--no-graph", action="store_true")
+    parser.add_argument("--skip-validation", action="store_true",
+                        help="keep going when the correctness gate fails (kernel experiments only)")
     parser.add_argument("--no-cpu-baseline", action="store_true")
     parser.add_argument("--cpu-layers", type=int, default=8)
     parser.add_argument("--cpu-seqs", type=int, default=4)

@@ -32,7 +32,7 @@ namespace {
 constexpr int kConsumerWarps = 8;
 constexpr int kConsumers = 32 * kConsumerWarps;  // 256 = fragment owners
 constexpr int kThreads = kConsumers + 32;        // + producer warp
-constexpr int kSlots = 4;
+constexpr int kSlots = 3;
 constexpr int kSlotBytes = kCodedMax;            // raw records are read in place
 constexpr int kPRow = 80;                        // bytes per (head, c) row of P, padded
 constexpr int kPBytes = 32 * kPRow;
@@ -77,6 +77,7 @@ struct DecodeParams {
   int64_t bt_stride;  // in entries
   int kvh, group, units;
   float scale_log2;
+  PipeConsts k;
 };
 
 // Plan (int32): [0] pages per chunk, [1] units in use, [2 + 2u] sequence and
@@ -298,7 +299,7 @@ __device__ __forceinline__ void consume(const DecodeParams& p, Smem& sm) {
           release(slot);
           raw_record_words(rec, tid, qk);
         } else {
-          coded_record_words(sm.slots[slot], sm.tabs[0], sm.esc, tid, [&] { release(slot); }, qk);
+          coded_record_words(sm.slots[slot], sm.tabs[0], sm.esc, tid, p.k, [&] { release(slot); }, qk);
         }
         ++r;
       }
@@ -377,28 +378,34 @@ __device__ __forceinline__ void consume(const DecodeParams& p, Smem& sm) {
         const int32_t vlen = sm.desc[slot].vlen;
         const uint4* pw = reinterpret_cast<const uint4*>(prow + (g * 4 + c) * kPRow);
         uint4 b;
-        // Tokens of a partial last page beyond the sequence are forced to
-        // zero so that stale bytes of an open block cannot reach the output.
-        const int rem = it.seq_len - page_tok0;
-        auto pvm = [&](int st, const uint32_t (&w)[4]) {
-          uint32_t a[4] = {w[0], w[1], w[2], w[3]};
-          if (rem < 128) {
-#pragma unroll
-            for (int x = 0; x < 4; ++x) {
-              const int t0 = 16 * st + 8 * (x & 1) + 2 * c;
-              if (t0 >= rem) a[x] = 0u;
-              else if (t0 + 1 >= rem) a[x] &= 0xffffu;
-            }
-          }
+        auto pv_word = [&](int st, const uint32_t (&w)[4]) {
           if ((st & 1) == 0) b = pw[st >> 1];
-          mma_16816(o, a[0], a[2], a[1], a[3], (st & 1) ? b.z : b.x, (st & 1) ? b.w : b.y);
+          mma_16816(o, w[0], w[2], w[1], w[3], (st & 1) ? b.z : b.x, (st & 1) ? b.w : b.y);
         };
         if (vlen > kVarCap || vlen < kHeaderBytes) {
           const uint8_t* rec = reinterpret_cast<const uint8_t*>(sm.desc[slot].addr);
           release(slot);
-          raw_record_words(rec, tid, pvm);
+          const int rem = it.seq_len - page_tok0;
+          if (rem < 128) {
+            // An open block (always a raw record) may hold stale bytes of the
+            // slot's previous owner beyond its last token: force them to zero
+            // so that no stale NaN / Inf can meet a zero probability.
+            raw_record_words(rec, tid, [&](int st, const uint32_t (&w)[4]) {
+              uint32_t a[4] = {w[0], w[1], w[2], w[3]};
+#pragma unroll
+              for (int x = 0; x < 4; ++x) {
+                const int t0 = 16 * st + 8 * (x & 1) + 2 * c;
+                if (t0 >= rem) a[x] = 0u;
+                else if (t0 + 1 >= rem) a[x] &= 0xffffu;
+              }
+              pv_word(st, a);
+            });
+          } else {
+            raw_record_words(rec, tid, pv_word);
+          }
         } else {
-          coded_record_words(sm.slots[slot], sm.tabs[1], sm.esc, tid, [&] { release(slot); }, pvm);
+          coded_record_words(sm.slots[slot], sm.tabs[1], sm.esc, tid, p.k, [&] { release(slot); },
+                             pv_word);
         }
         ++r;
       }
@@ -670,6 +677,7 @@ int fp_fused_decode(const void* q, int64_t q_stride, const int64_t* rec_addr,
   p.group = group;
   p.units = units;
   p.scale_log2 = scale * 1.4426950408889634f;
+  p.k = pipe_consts();
   const int smem = (int)sizeof(Smem);
   if (int rc = cuda_status(cudaFuncSetAttribute(decode_attn_kernel,
                                                 cudaFuncAttributeMaxDynamicSharedMemorySize, smem),

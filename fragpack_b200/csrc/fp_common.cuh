@@ -28,13 +28,42 @@ constexpr int kHeaderBytes = 48;
 constexpr int kPrimaryDirect = 7;
 constexpr int kTableEntries = 22;
 constexpr int kMaxWarpRaw = 32;
-// Expanded escape bytes of one record: warp w keeps escape ordinal x at byte
-// 32 w + x.  The 32-byte shift keeps the 8-byte groups that neighbouring warps
-// write at their range boundaries disjoint.  Ordinals are clamped to
-// kEscOrdinalCap when they are written, and readers reach at most 2048 + 12
-// bytes further, so a malformed record cannot leave the buffer.
+// Expanded escapes of one record.  Escape ordinal x of warp w owns the 4-byte
+// window (escape bytes x .. x + 3) at byte kEscPad + 64 w + 4 x, so a word reads
+// its next eight escape bytes as the two aligned windows x and x + 4.  The
+// 64-byte shift per warp keeps the 8-window groups that neighbouring warps
+// write at their range boundaries disjoint; the front pad takes the raw patches
+// that reach three windows back.  Ordinals are clamped to kEscOrdinalCap, so a
+// malformed record cannot leave the buffer.
 constexpr int kEscOrdinalCap = 4096;
-constexpr int kEscBytes = 32 * 7 + kEscOrdinalCap + 2048 + 32;  // 6400
+constexpr int kEscPad = 16;
+constexpr int kEscBytes = kEscPad + 64 * 7 + 4 * (kEscOrdinalCap + 8) + 32;  // 16912
+
+// Multipliers that are only known at run time, so that shifts and adds written
+// as integer multiply-adds stay on the multiply pipe instead of the (half-rate,
+// saturated) ALU pipe: x >> 16 = hi(x * 2^16), x >> 1 = hi(x * 2^31).
+struct PipeConsts {
+  uint32_t one, four, two16, two29, two30, two31;
+};
+__host__ __device__ inline PipeConsts pipe_consts() {
+  return PipeConsts{1u, 4u, 1u << 16, 1u << 29, 1u << 30, 1u << 31};
+}
+
+__device__ __forceinline__ uint32_t mul_hi(uint32_t a, uint32_t b) {
+  uint32_t r;
+  asm("mul.hi.u32 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+  return r;
+}
+__device__ __forceinline__ uint32_t mad_hi(uint32_t a, uint32_t b, uint32_t c) {
+  uint32_t r;
+  asm("mad.hi.u32 %0, %1, %2, %3;" : "=r"(r) : "r"(a), "r"(b), "r"(c));
+  return r;
+}
+__device__ __forceinline__ uint32_t mad_lo(uint32_t a, uint32_t b, uint32_t c) {
+  uint32_t r;
+  asm("mad.lo.u32 %0, %1, %2, %3;" : "=r"(r) : "r"(a), "r"(b), "r"(c));
+  return r;
+}
 
 __device__ __forceinline__ uint32_t smem_addr(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
@@ -106,13 +135,17 @@ __device__ __forceinline__ void raw_record_words(const uint8_t* rec, int tid, Em
 // `rec` by this warp has been made (dense part held in registers, escapes
 // expanded), so the caller may hand the record's buffer back to a producer.
 //
-// Follows the decoder the format was designed for
-// (fragpack/ops/fragpack_common.cuh:92-186) with a byte-per-escape scratch
-// instead of sliding windows.
+// Phases: (1) the warp expands its escape nibbles through the extended table
+// into sliding windows and patches raw scalars; (2) every owner counts its
+// escapes and a warp scan gives its first ordinal; (3) per word: primary codes
+// through prmt over the 8-byte table, escape bytes picked from two windows by
+// exclusive rank and merged, low and high bytes interleaved.
+// The scheme is the one the format was laid out for
+// (fragpack/ops/fragpack_common.cuh:92-186).
 template <typename Released, typename Emit>
 __device__ __forceinline__ void coded_record_words(const uint8_t* rec, const HeadTables& tab,
-                                                   uint8_t* esc, int tid, Released&& released,
-                                                   Emit&& emit) {
+                                                   uint8_t* esc, int tid, const PipeConsts& k,
+                                                   Released&& released, Emit&& emit) {
   const int lane = tid & 31, warp = tid >> 5;
   uint4 low[4];
   uint2 sym[3];
@@ -125,16 +158,22 @@ __device__ __forceinline__ void coded_record_words(const uint8_t* rec, const Hea
   const uint8_t* var = rec + kDenseBytes;
   const uint16_t* h16 = reinterpret_cast<const uint16_t*>(var);
   const uint32_t* h32 = reinterpret_cast<const uint32_t*>(var);
-  uint8_t* mine = esc + 32 * warp;
+  uint8_t* mine = esc + kEscPad + 64 * warp;
   const int first_esc = min((int)h16[8 + warp], kEscOrdinalCap);
   {
     const int end_esc = min(warp < 7 ? (int)h16[9 + warp] : (int)h32[0], kEscOrdinalCap);
     const uint32_t* nibbles = reinterpret_cast<const uint32_t*>(var + kHeaderBytes);
+    const uint4 ext = tab.ext;
     __syncwarp();  // the previous record's readers of `mine` are done
-    for (int k = (first_esc >> 3) + lane; 8 * k < end_esc; k += 32) {
-      const uint32_t n = nibbles[k];
-      *reinterpret_cast<uint2*>(mine + 8 * k) =
-          make_uint2(extended_bytes(tab.ext, n), extended_bytes(tab.ext, n >> 16));
+    for (int g8 = (first_esc >> 3) + lane; 8 * g8 < end_esc; g8 += 32) {
+      const uint32_t n0 = nibbles[g8], n1 = nibbles[g8 + 1];
+      const uint32_t b0 = extended_bytes(ext, n0), b1 = extended_bytes(ext, mul_hi(n0, k.two16));
+      const uint32_t b2 = extended_bytes(ext, n1);
+      uint4* dst = reinterpret_cast<uint4*>(mine + 32 * g8);
+      dst[0] = make_uint4(b0, __funnelshift_r(b0, b1, 8), __funnelshift_r(b0, b1, 16),
+                          __funnelshift_r(b0, b1, 24));
+      dst[1] = make_uint4(b1, __funnelshift_r(b1, b2, 8), __funnelshift_r(b1, b2, 16),
+                          __funnelshift_r(b1, b2, 24));
     }
     // At most kMaxWarpRaw raw scalars per warp: one patch per lane.
     const int first_raw = h16[16 + warp];
@@ -147,12 +186,17 @@ __device__ __forceinline__ void coded_record_words(const uint8_t* rec, const Hea
     }
     __syncwarp();
     released();
-    if (lane < n_raw) mine[min(patch & 0xffffu, (uint32_t)kEscOrdinalCap)] = (uint8_t)(patch >> 16);
+    if (lane < n_raw) {
+      // The raw byte of ordinal x is byte j of window x - j.
+      const int x = min((int)(patch & 0xffffu), kEscOrdinalCap);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) mine[4 * (x - j) + j] = (uint8_t)(patch >> 16);
+    }
   }
 
-  // Escape flags (bit 3 of each nibble) of the eight words and their count.
+  // Selector words (3-bit codes, bit 3 clear) of the eight words; escapes are
+  // the nibbles equal to 7.
   uint32_t sel[8];
-  int count = 0;
 #pragma unroll
   for (int gi = 0; gi < 2; ++gi) {
     const uint32_t w0 = gi == 0 ? sym[0].x : sym[1].y;
@@ -161,33 +205,44 @@ __device__ __forceinline__ void coded_record_words(const uint8_t* rec, const Hea
     sel[4 * gi + 0] = w0 & 0x77777777u;
     sel[4 * gi + 1] = w1 & 0x77777777u;
     sel[4 * gi + 2] = w2 & 0x77777777u;
-    sel[4 * gi + 3] =
-        ((w0 >> 3) & 0x11111111u) | ((w1 >> 2) & 0x22222222u) | ((w2 >> 1) & 0x44444444u);
-#pragma unroll
-    for (int k = 0; k < 4; ++k)
-      count += __popc((sel[4 * gi + k] + 0x11111111u) & 0x88888888u);
+    // Bit 3 of the three stored words carries the fourth word, one bit each.
+    sel[4 * gi + 3] = (mul_hi(w0, k.two29) & 0x11111111u) | (mul_hi(w1, k.two30) & 0x22222222u) |
+                      (mul_hi(w2, k.two31) & 0x44444444u);
   }
-  int ordinal = first_esc + warp_exclusive_sum(count, lane);
+  int count = 0;
+#pragma unroll
+  for (int gi = 0; gi < 2; ++gi) {
+    // The flags of four words sit on distinct bits once shifted by 0..3.
+    const uint32_t f0 = mad_lo(sel[4 * gi + 0], k.one, 0x11111111u) & 0x88888888u;
+    const uint32_t f1 = mad_lo(sel[4 * gi + 1], k.one, 0x11111111u) & 0x88888888u;
+    const uint32_t f2 = mad_lo(sel[4 * gi + 2], k.one, 0x11111111u) & 0x88888888u;
+    const uint32_t f3 = mad_lo(sel[4 * gi + 3], k.one, 0x11111111u) & 0x88888888u;
+    count += __popc(f0 | mul_hi(f1, k.two31) | mul_hi(f2, k.two30) | mul_hi(f3, k.two29));
+  }
+  // A thread consumes at most 64 escapes: clamping its first ordinal bounds
+  // every window read below.
+  const int ordinal = min(first_esc + warp_exclusive_sum(count, lane), kEscOrdinalCap - 64);
   __syncwarp();  // expansion and patches visible to the whole warp
 
-  const uint32_t* mine32 = reinterpret_cast<const uint32_t*>(mine);
+  uint32_t window = smem_addr(mine) + 4u * (uint32_t)ordinal;
 #pragma unroll
   for (int st = 0; st < 8; ++st) {
-    const uint32_t s = sel[st], f = (s + 0x11111111u) & 0x88888888u;
+    const uint32_t s = sel[st];
+    const uint32_t f = mad_lo(s, k.one, 0x11111111u) & 0x88888888u;
     uint32_t ha = prmt(tab.p0, tab.p1, s);
-    uint32_t hb = prmt(tab.p0, tab.p1, s >> 16);
-    {
-      // The next eight escape bytes from `ordinal` on, unaligned.
-      const uint32_t* at = mine32 + (ordinal >> 2);
-      const uint32_t shift = (ordinal & 3) * 8;
-      const uint32_t a = at[0], b = at[1], c = at[2];
-      const uint32_t e0 = __funnelshift_r(a, b, shift), e1 = __funnelshift_r(b, c, shift);
-      ordinal += __popc(f);
-      // Nibble n of `rank` = escapes among nibbles below n.
-      const uint32_t rank = f * 0x02222222u;
-      ha = prmt(ha, prmt(e0, e1, rank), (f >> 1) + 0x3210u);
-      hb = prmt(hb, prmt(e0, e1, rank >> 16), (f >> 17) + 0x3210u);
-    }
+    uint32_t hb = prmt(tab.p0, tab.p1, mul_hi(s, k.two16));
+    uint32_t e0, e1;
+    asm("ld.shared.u32 %0, [%2];\n\tld.shared.u32 %1, [%2+16];"
+        : "=r"(e0), "=r"(e1)
+        : "r"(window)
+        : "memory");
+    window = mad_lo((uint32_t)__popc(f), k.four, window);
+    // Nibble n of `rank` = escapes among the nibbles below n.
+    const uint32_t rank = f * 0x02222222u;
+    // Selector nibble n: n keeps the table byte, 4 + n takes the escape byte.
+    const uint32_t pick = mad_hi(f, k.two31, 0x32103210u);
+    ha = prmt(ha, prmt(e0, e1, rank), pick);
+    hb = prmt(hb, prmt(e0, e1, mul_hi(rank, k.two16)), mul_hi(pick, k.two16));
     const uint4& lw = low[st >> 1];
     const uint32_t la = (st & 1) ? lw.z : lw.x;
     const uint32_t lb = (st & 1) ? lw.w : lw.y;

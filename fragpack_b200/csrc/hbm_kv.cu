@@ -571,13 +571,13 @@ encode_records_kernel(const uint8_t* raw, const uint8_t* rank_of, const int32_t*
 // One record -> token-major rows of `row_bytes` stride starting at `dst`.
 __device__ __forceinline__ void decode_to_rows(const uint8_t* rec, int vlen, const HeadTables& tab,
                                                int kv, uint8_t* tile, uint8_t* esc, uint8_t* dst,
-                                               int64_t row_bytes, int tid) {
+                                               int64_t row_bytes, int tid, const PipeConsts& k) {
   const OwnerCoords o(tid);
   auto emit = [&](int st, const uint32_t (&w)[4]) { word_to_tile(tile, kv, o, st, w); };
   if (vlen > kVarCap)
     raw_record_words(rec, tid, emit);
   else
-    coded_record_words(rec, tab, esc, tid, [] {}, emit);
+    coded_record_words(rec, tab, esc, tid, k, [] {}, emit);
   __syncthreads();
   tile_store(tile, dst, row_bytes, tid);
 }
@@ -587,26 +587,27 @@ constexpr int kDecodeSmem = kTileBytes + kEscBytes;
 // Prefill decompressor: grid (pages, 2 H).  hbm_kv.cu:452-494.
 __global__ void __launch_bounds__(kOwners)
 gather_kernel(const int32_t* blocks, const int64_t* rec_addr, const int32_t* rec_len,
-              const int32_t* plut, const uint8_t* slut, uint8_t* wk, uint8_t* wv, int H) {
+              const int32_t* plut, const uint8_t* slut, uint8_t* wk, uint8_t* wv, int H,
+              PipeConsts k) {
   extern __shared__ __align__(16) uint8_t dyn[];
   const int rec = blockIdx.y, kv = rec / H, head = rec % H;
   const int64_t idx = (int64_t)blocks[blockIdx.x] * 2 * H + rec;
   const HeadTables tab = load_tables(plut, slut, rec);
   uint8_t* dst = (kv == 0 ? wk : wv) + ((int64_t)blockIdx.x * 128 * H + head) * 256;
   decode_to_rows(reinterpret_cast<const uint8_t*>(rec_addr[idx]), rec_len[idx], tab, kv, dyn,
-                 dyn + kTileBytes, dst, (int64_t)H * 256, threadIdx.x);
+                 dyn + kTileBytes, dst, (int64_t)H * 256, threadIdx.x, k);
 }
 
 // Batch decoder: grid = records.
 __global__ void __launch_bounds__(kOwners)
 decode_records_kernel(const uint8_t* recs, int64_t rec_stride, const int32_t* rec_len,
                       const int32_t* plut, const uint8_t* slut, const int32_t* table_index,
-                      const int32_t* kv, uint8_t* out) {
+                      const int32_t* kv, uint8_t* out, PipeConsts k) {
   extern __shared__ __align__(16) uint8_t dyn[];
   const int64_t i = blockIdx.x;
   const HeadTables tab = load_tables(plut, slut, table_index ? table_index[i] : (int32_t)i);
   decode_to_rows(recs + i * rec_stride, rec_len[i], tab, kv[i], dyn, dyn + kTileBytes,
-                 out + i * kRawRecord, 256, threadIdx.x);
+                 out + i * kRawRecord, 256, threadIdx.x, k);
 }
 
 int check_store(const fp_store* st) {
@@ -707,7 +708,7 @@ int fp_hbm_gather(const int32_t* blocks, int64_t n, const int64_t* rec_addr,
   if (allowed) return allowed;
   gather_kernel<<<dim3((unsigned)n, 2 * kv_heads), kOwners, kDecodeSmem, (cudaStream_t)stream>>>(
       blocks, rec_addr, rec_len, plut, slut, static_cast<uint8_t*>(wk), static_cast<uint8_t*>(wv),
-      kv_heads);
+      kv_heads, pipe_consts());
   FP_LAUNCH_CHECK("gather_kernel");
   return FP_OK;
 }
@@ -744,7 +745,8 @@ int fp_decode_records(const uint8_t* recs, int64_t rec_stride, const int32_t* re
   static int allowed = allow_smem(decode_records_kernel, kDecodeSmem);
   if (allowed) return allowed;
   decode_records_kernel<<<(unsigned)n, kOwners, kDecodeSmem, (cudaStream_t)stream>>>(
-      recs, rec_stride, rec_len, plut, slut, table_index, kv, static_cast<uint8_t*>(out));
+      recs, rec_stride, rec_len, plut, slut, table_index, kv, static_cast<uint8_t*>(out),
+      pipe_consts());
   FP_LAUNCH_CHECK("decode_records_kernel");
   return FP_OK;
 }

@@ -12,12 +12,15 @@ from __future__ import annotations
 
 import ctypes
 import functools
+import os
 from pathlib import Path
 
 import torch
 
 _DIR = Path(__file__).resolve().parent
-LIBRARY = _DIR / "libfragpack_b200.so"
+# FRAGPACK_B200_LIBRARY points at another build of the same C ABI (for example
+# one compiled with different flags); by default the in-tree library is used.
+LIBRARY = Path(os.environ.get("FRAGPACK_B200_LIBRARY") or _DIR / "libfragpack_b200.so")
 
 c_i32, c_i64, c_f32, c_ptr = ctypes.c_int32, ctypes.c_int64, ctypes.c_float, ctypes.c_void_p
 
