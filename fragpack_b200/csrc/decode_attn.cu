@@ -46,7 +46,9 @@ struct SlotDesc {
 
 struct Smem {
   __align__(128) uint8_t slots[kSlots][kSlotBytes];
-  __align__(16) uint8_t esc[kEscBytes];
+  // K and V records expand their escapes into separate buffers: the V decode of
+  // a page and the K decode of the next one run without a barrier between them.
+  __align__(16) uint8_t esc[2][kEscBytes];
   __align__(16) uint8_t p[2][kPBytes];
   __align__(16) float ref[2][kConsumerWarps][8];
   __align__(16) int flag[2][kConsumerWarps];
@@ -60,6 +62,9 @@ struct Smem {
   __align__(8) uint64_t empty[kSlots];
   int abort;
 };
+
+// Two CTAs must fit one SM: 228 KB per SM, 1 KB reserved per CTA.
+static_assert(sizeof(Smem) <= (228 * 1024) / 2 - 1024, "Smem too large for two CTAs per SM");
 
 struct DecodeParams {
   const uint32_t* q;
@@ -299,7 +304,7 @@ __device__ __forceinline__ void consume(const DecodeParams& p, Smem& sm) {
           release(slot);
           raw_record_words(rec, tid, qk);
         } else {
-          coded_record_words(sm.slots[slot], sm.tabs[0], sm.esc, tid, p.k, [&] { release(slot); }, qk);
+          coded_record_words(sm.slots[slot], sm.tabs[0], sm.esc[0], tid, p.k, [&] { release(slot); }, qk);
         }
         ++r;
       }
@@ -404,7 +409,7 @@ __device__ __forceinline__ void consume(const DecodeParams& p, Smem& sm) {
             raw_record_words(rec, tid, pv_word);
           }
         } else {
-          coded_record_words(sm.slots[slot], sm.tabs[1], sm.esc, tid, p.k, [&] { release(slot); },
+          coded_record_words(sm.slots[slot], sm.tabs[1], sm.esc[1], tid, p.k, [&] { release(slot); },
                              pv_word);
         }
         ++r;

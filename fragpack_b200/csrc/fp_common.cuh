@@ -35,9 +35,10 @@ constexpr int kMaxWarpRaw = 32;
 // write at their range boundaries disjoint; the front pad takes the raw patches
 // that reach three windows back.  Ordinals are clamped to kEscOrdinalCap, so a
 // malformed record cannot leave the buffer.
-constexpr int kEscOrdinalCap = 4096;
+// A coded record holds at most (2048 - 48) * 2 = 4000 escapes.
+constexpr int kEscOrdinalCap = 4000;
 constexpr int kEscPad = 16;
-constexpr int kEscBytes = kEscPad + 64 * 7 + 4 * (kEscOrdinalCap + 8) + 32;  // 16912
+constexpr int kEscBytes = kEscPad + 64 * 7 + 4 * (kEscOrdinalCap + 8) + 32;  // 16528
 
 // Multipliers that are only known at run time, so that shifts and adds written
 // as integer multiply-adds stay on the multiply pipe instead of the (half-rate,
@@ -130,8 +131,10 @@ __device__ __forceinline__ void raw_record_words(const uint8_t* rec, int tid, Em
 // for st = 0..7 where w[0..3] are the BF16 pairs (j0 f0, j0 f1, j1 f0, j1 f1).
 //
 // `rec` may be shared or global memory.  `esc` is a kEscBytes scratch in
-// shared memory; each warp touches only its own part of it, so only warp-level
-// synchronisation happens in here.  `released()` is called once every read of
+// shared memory.  Within one record each warp touches only its own part of it,
+// so only warp-level synchronisation happens in here; but the parts move with
+// the record's escape prefixes, so two records may share one scratch only if a
+// block-wide barrier separates their decodes.  `released()` is called once every read of
 // `rec` by this warp has been made (dense part held in registers, escapes
 // expanded), so the caller may hand the record's buffer back to a producer.
 //

@@ -215,3 +215,27 @@ def test_graph_replans_padding_and_reuses_plan_across_layers(
         graph.replay()
         _check_outputs(queries, outputs, source, table, lengths)
     assert decode_status(workspace, units) == 0
+
+
+@pytest.mark.parametrize("units_policy", ["auto", "minimum"])
+def test_repeated_launches_are_bitwise_identical(encoded_store, units_policy: str) -> None:
+    """The same launch twenty times: any difference would be a race between warps."""
+    store, _arenas, source = encoded_store
+    batch = 269
+    sms = torch.cuda.get_device_properties(source.device).multi_processor_count
+    units = decode_units(batch, HEADS, sms) if units_policy == "auto" else batch
+    workspace = _workspace(units, source.device)
+    table = torch.from_numpy(_block_table(batch)).to(source.device)
+    lengths = torch.from_numpy(_ragged_lengths(batch)).to(source.device)
+    generator = torch.Generator(device=source.device).manual_seed(77)
+    q = torch.randn(batch, HEADS * GQA, DIM, dtype=torch.bfloat16, device=source.device,
+                    generator=generator)
+    tabs = RecordTables(*store.layer_tables(0))
+    first = None
+    for _ in range(20):
+        out = torch.full_like(q, float("nan"))
+        decode_attention(q, tabs, table, lengths, SCALE, units, out, workspace, replan=True)
+        if first is None:
+            first = out
+        else:
+            assert torch.equal(out.view(torch.int16), first.view(torch.int16))
