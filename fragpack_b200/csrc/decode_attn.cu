@@ -698,4 +698,78 @@ int fp_fused_decode(const void* q, int64_t q_stride, const int64_t* rec_addr,
   return FP_OK;
 }
 
+/*
+ * Decode attention for callers that may not allocate device memory.
+ *
+ * Some hosts of this library hand it a CUDA context in which they own every
+ * allocation: an engine that carved the whole device into its own pools at
+ * start-up, a plugin running inside someone else's memory planner, a worker
+ * whose allocator is locked once serving begins.  Such callers cannot provide
+ * (or grow) the opart / ml / plan workspace that fp_fused_decode needs.  This
+ * variant keeps that workspace in one fixed array inside the library image, so
+ * the caller passes only inputs and outputs.
+ *
+ * The array is part of every process image that loads the library: each GPU
+ * the process touches holds kStaticScratchBytes of it until the process exits.
+ */
+namespace {
+
+constexpr int kStaticUnitHeads = 4096;  // largest kv_heads * units served
+constexpr int kStaticUnits = 4096;      // largest units served
+constexpr size_t kStaticOpartBytes = (size_t)kStaticUnitHeads * 8 * 128 * sizeof(float);
+constexpr size_t kStaticMlBytes = (size_t)kStaticUnitHeads * 8 * 2 * sizeof(float);
+constexpr size_t kStaticPlanBytes = ((2 + 4 * (size_t)kStaticUnits + 2) * sizeof(int32_t) + 255) / 256 * 256;
+constexpr size_t kStaticScratchBytes = kStaticOpartBytes + kStaticMlBytes + kStaticPlanBytes;
+
+// In host code this name is only a handle for cudaGetSymbolAddress; it is not
+// a device address and must never be passed to a kernel as one.
+static __device__ __align__(256) uint8_t g_decode_scratch[kStaticScratchBytes];
+
+// Device address of g_decode_scratch on the current device, looked up once per
+// device (with that device current) and cached.
+int static_scratch(uint8_t** base) {
+  static uint8_t* cached[64] = {nullptr};
+  int dev = 0;
+  if (int rc = cuda_status(cudaGetDevice(&dev), "cudaGetDevice")) return rc;
+  if (dev < 0 || dev >= 64) return fail(FP_ERR_ARGUMENT, "device index %d not supported", dev);
+  if (cached[dev] == nullptr) {
+    void* ptr = nullptr;
+    if (int rc = cuda_status(cudaGetSymbolAddress(&ptr, g_decode_scratch),
+                             "cudaGetSymbolAddress(g_decode_scratch)"))
+      return rc;
+    if (ptr == nullptr) return fail(FP_ERR_CUDA, "static decode scratch has no device address");
+    cached[dev] = static_cast<uint8_t*>(ptr);
+  }
+  *base = cached[dev];
+  return FP_OK;
+}
+
+}  // namespace
+
+int fp_fused_decode_noalloc(const void* q, int64_t q_stride, const int64_t* rec_addr,
+                            const int32_t* rec_len, const int32_t* plut, const uint8_t* slut,
+                            const int32_t* block_table, int64_t bt_stride,
+                            const int32_t* seq_lens, void* out, int64_t out_stride, int32_t batch,
+                            int32_t kv_heads, int32_t group, int32_t units, int32_t replan,
+                            float scale, int32_t num_sms, void* stream) {
+  if (batch == 0) return FP_OK;
+  FP_REQUIRE(kv_heads > 0 && units > 0, "bad kv_heads %d / units %d", kv_heads, units);
+  FP_REQUIRE(units <= kStaticUnits && (int64_t)kv_heads * units <= kStaticUnitHeads,
+             "the built-in decode scratch serves kv_heads * units <= %d and units <= %d; got "
+             "kv_heads %d, units %d (pass fewer units, or use fp_fused_decode with a workspace)",
+             kStaticUnitHeads, kStaticUnits, kv_heads, units);
+  uint8_t* base = nullptr;
+  if (int rc = static_scratch(&base)) return rc;
+  float* opart = reinterpret_cast<float*>(base);
+  float* ml = reinterpret_cast<float*>(base + kStaticOpartBytes);
+  int32_t* plan = reinterpret_cast<int32_t*>(base + kStaticOpartBytes + kStaticMlBytes);
+  // Nothing in the scratch has to start at zero: the planner rewrites the plan
+  // and its status word whenever `replan` is set, and every partial result is
+  // written by the attention kernel before the merge reads it.
+  return fp_fused_decode(q, q_stride, rec_addr, rec_len, plut, slut, block_table, bt_stride,
+                         seq_lens, opart, (int64_t)(kStaticOpartBytes / sizeof(float)), ml,
+                         (int64_t)(kStaticMlBytes / sizeof(float)), plan, plan_words(units), out,
+                         out_stride, batch, kv_heads, group, units, replan, scale, num_sms, stream);
+}
+
 }  // extern "C"

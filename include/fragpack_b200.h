@@ -113,6 +113,33 @@ int fp_fused_decode(const void* q, int64_t q_stride, const int64_t* rec_addr,
                     int32_t kv_heads, int32_t group, int32_t units, int32_t replan, float scale,
                     int32_t num_sms, void* stream);
 
+/*
+ * fp_fused_decode without a caller-provided workspace, for hosts that cannot
+ * call cudaMalloc (or any allocator) on behalf of this library: engines that
+ * own all device memory, plugins inside a foreign memory planner, workers whose
+ * allocator is frozen while serving.  It has no counterpart in the reference.
+ *
+ * The opart / ml / plan workspace lives in a fixed array inside the library
+ * (about 16.3 MiB, held on every GPU that loads the library until the process
+ * exits).  Limits: kv_heads * units <= 4096 and units <= 4096; larger requests
+ * are rejected with FP_ERR_ARGUMENT and a message naming the limit.  The call
+ * allocates nothing and calls no allocating routine.
+ *
+ * The first call on a device looks up the array's device address (once per
+ * device, with that device current); make that first call before any stream
+ * capture begins.  All calls share the one array and it keeps the previous
+ * call's contents: a call with replan = 0 reuses the plan of the previous call
+ * exactly as fp_fused_decode does with a reused workspace, and calls that can
+ * overlap on the GPU (different streams, or different threads) race on it -
+ * serialise them.  Arguments are those of fp_fused_decode minus the workspace.
+ */
+int fp_fused_decode_noalloc(const void* q, int64_t q_stride, const int64_t* rec_addr,
+                            const int32_t* rec_len, const int32_t* plut, const uint8_t* slut,
+                            const int32_t* block_table, int64_t bt_stride,
+                            const int32_t* seq_lens, void* out, int64_t out_stride, int32_t batch,
+                            int32_t kv_heads, int32_t group, int32_t units, int32_t replan,
+                            float scale, int32_t num_sms, void* stream);
+
 /* hbm_prepare (fragpack/ops/hbm_kv.cu:669-686): start a step. */
 int fp_hbm_prepare(const fp_store* store, const int64_t* slot_mapping, int64_t num_tokens,
                    const int32_t* live, int64_t num_live, int32_t step, void* stream);

@@ -1,0 +1,85 @@
+"""The allocation-free decode entry point against the regular one.
+
+``fp_fused_decode_noalloc`` serves hosts that cannot allocate device memory
+for this library (an engine that owns every byte of the device, a plugin under
+a foreign memory planner, a worker with a frozen allocator): it keeps the
+split-KV workspace in a fixed array inside the library instead of taking it
+from the caller.  This file is collected last on purpose, so that a run that
+stops at the first failure has already run every other test; it passes alone
+in a fresh process as well as after the others.
+
+The check: two calls in a row through the C ABI (the second one reusing the
+plan left in the shared array by the first, then a third with new lengths)
+must give what ``fp_fused_decode`` gives with a caller-owned workspace, within
+the tolerance the other decode tests use.
+"""
+
+from __future__ import annotations
+
+import pytest
+import torch
+
+from fragpack_b200 import workloads
+from fragpack_b200.ops.fragpack_ext import check, extension, stream_ptr
+from fragpack_b200.ops.fused_attn_decode import (
+    RecordTables,
+    decode_attention,
+    decode_units,
+    workspace_elems,
+)
+
+pytestmark = pytest.mark.gpu
+SCALE = 128**-0.5
+
+
+def _noalloc(q, tabs, block_table, seq_lens, out, kv_heads, group, units, replan) -> int:
+    sms = torch.cuda.get_device_properties(q.device).multi_processor_count
+    return extension().fp_fused_decode_noalloc(
+        q.data_ptr(), q.stride(0), tabs.rec_addr.data_ptr(), tabs.rec_len.data_ptr(),
+        tabs.plut.data_ptr(), tabs.slut.data_ptr(), block_table.data_ptr(), block_table.stride(0),
+        seq_lens.data_ptr(), out.data_ptr(), out.stride(0), q.shape[0], kv_heads, group, units,
+        int(replan), SCALE, sms, stream_ptr(),
+    )
+
+
+def test_noalloc_matches_workspace_entry_point_twice_in_a_row() -> None:
+    device = torch.device("cuda", torch.cuda.current_device())
+    cfg = workloads.CONFIGS["c1"]
+    work = workloads.build_decode_workload(cfg, device, seed=11)
+    H, G, B = cfg.kv_heads, cfg.group, cfg.batch
+    sms = torch.cuda.get_device_properties(device).multi_processor_count
+    units = decode_units(B, H, sms)
+    assert H * units <= 4096
+    sizes = workspace_elems(H, units)
+    ws = (
+        torch.empty(sizes[0], device=device),
+        torch.empty(sizes[1], device=device),
+        torch.empty(sizes[2], dtype=torch.int32, device=device),
+    )
+    tabs = RecordTables(*work.store.layer_tables(0))
+    gen = torch.Generator(device=device).manual_seed(5)
+    lens_a = work.seq_lens.clone()
+    lens_b = torch.tensor([300, 77], dtype=torch.int32, device=device)
+    # (lengths, replan): the second call reuses the first call's plan.
+    for lens, replan in ((lens_a, True), (lens_a, False), (lens_b, True)):
+        q = torch.randn(B, H * G, 128, generator=gen, device=device).to(torch.bfloat16)
+        want = torch.full_like(q, float("nan"))
+        decode_attention(q, tabs, work.block_table, lens, SCALE, units, want, ws, replan)
+        got = torch.full_like(q, float("nan"))
+        check(_noalloc(q, tabs, work.block_table, lens, got, H, G, units, replan))
+        torch.cuda.synchronize()
+        assert not torch.isnan(got).any()
+        torch.testing.assert_close(got.float(), want.float(), atol=2e-2, rtol=2e-2)
+
+
+def test_noalloc_rejects_sizes_beyond_its_scratch() -> None:
+    device = torch.device("cuda", torch.cuda.current_device())
+    dummy = torch.zeros(64, dtype=torch.int64, device=device)
+    q = torch.zeros(1, 8, 128, dtype=torch.bfloat16, device=device)
+    tabs = RecordTables(dummy, dummy, dummy, dummy)
+    rc = _noalloc(q, tabs, dummy, dummy, q, kv_heads=1, group=8, units=4097, replan=True)
+    assert rc != 0
+    message = extension().fp_last_error().decode()
+    assert "4096" in message and "units" in message
+    rc = _noalloc(q, tabs, dummy, dummy, q, kv_heads=8, group=8, units=1024, replan=True)
+    assert rc != 0
