@@ -286,14 +286,12 @@ def run_ours(args) -> dict:
     ]
     outputs = [torch.full_like(q, float("nan")) for q in queries]
     tabs = [RecordTables(*work.store.layer_tables(layer)) for layer in range(layers)]
-    gathered = (
-        [torch.empty(world, B, H * G, 128, dtype=torch.bfloat16, device=device) for _ in range(layers)]
-        if world > 1 else None
-    )
-    oproj_in = (
-        [torch.empty(B, world * H * G, 128, dtype=torch.bfloat16, device=device) for _ in range(layers)]
-        if world > 1 else None
-    )
+    gather = None
+    if world > 1:
+        from fragpack_b200.ops.tp import HeadGather
+
+        gather = HeadGather(B, H * G, torch.bfloat16, device)
+    oproj_in = None
 
     def attend(layer: int) -> None:
         decode_attention(queries[layer], tabs[layer], work.block_table, work.seq_lens, SCALE,
@@ -302,10 +300,10 @@ def run_ours(args) -> dict:
     def step() -> None:
         for layer in range(layers):
             attend(layer)
-            if world > 1:
+            if gather is not None:
                 # Per-head outputs -> o_proj input layout [B, Hq, 128] on every rank.
-                dist.all_gather_into_tensor(gathered[layer], outputs[layer])
-                oproj_in[layer].view(B, world, H * G, 128).copy_(gathered[layer].transpose(0, 1))
+                nonlocal oproj_in
+                oproj_in = gather(outputs[layer])
 
     # Correctness gate before any timing (outputs start as NaN).
     step()
