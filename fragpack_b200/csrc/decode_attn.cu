@@ -105,16 +105,18 @@ __device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
                "r"(bytes)
                : "memory");
 }
-__device__ __forceinline__ bool mbar_try(uint64_t* bar, uint32_t parity) {
+// One try: the hardware may suspend the thread for up to `hint_ns` while the
+// phase is incomplete, so a waiting warp does not burn issue slots polling.
+__device__ __forceinline__ bool mbar_try(uint64_t* bar, uint32_t parity, uint32_t hint_ns) {
   uint32_t done;
   asm volatile(
       "{\n"
       ".reg .pred p;\n"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n"
       "selp.u32 %0, 1, 0, p;\n"
       "}\n"
       : "=r"(done)
-      : "r"(smem_addr(bar)), "r"(parity)
+      : "r"(smem_addr(bar)), "r"(parity), "r"(hint_ns)
       : "memory");
   return done != 0;
 }
@@ -140,8 +142,8 @@ __device__ __noinline__ bool wait_slow(uint64_t* bar, uint32_t parity, volatile 
   const long long t0 = clock64();
   for (;;) {
 #pragma unroll 1
-    for (int i = 0; i < 64; ++i)
-      if (mbar_try(bar, parity)) return true;
+    for (int i = 0; i < 16; ++i)
+      if (mbar_try(bar, parity, 20000u)) return true;
     if (*abort) return false;
     if (clock64() - t0 > kWaitCycles) {
       *abort = 1;
@@ -152,7 +154,7 @@ __device__ __noinline__ bool wait_slow(uint64_t* bar, uint32_t parity, volatile 
 }
 __device__ __forceinline__ bool bounded_wait(uint64_t* bar, uint32_t parity, volatile int* abort,
                                              int32_t* status) {
-  if (mbar_try(bar, parity)) return true;
+  if (mbar_try(bar, parity, 2000u)) return true;
   return wait_slow(bar, parity, abort, status);
 }
 
@@ -304,7 +306,7 @@ __device__ __forceinline__ void consume(const DecodeParams& p, Smem& sm) {
           release(slot);
           raw_record_words(rec, tid, qk);
         } else {
-          coded_record_words(sm.slots[slot], sm.tabs[0], sm.esc[0], tid, p.k, [&] { release(slot); }, qk);
+          coded_record_words(sm.slots[slot], vlen, sm.tabs[0], sm.esc[0], tid, p.k, [&] { release(slot); }, qk);
         }
         ++r;
       }
@@ -409,7 +411,7 @@ __device__ __forceinline__ void consume(const DecodeParams& p, Smem& sm) {
             raw_record_words(rec, tid, pv_word);
           }
         } else {
-          coded_record_words(sm.slots[slot], sm.tabs[1], sm.esc[1], tid, p.k, [&] { release(slot); },
+          coded_record_words(sm.slots[slot], vlen, sm.tabs[1], sm.esc[1], tid, p.k, [&] { release(slot); },
                              pv_word);
         }
         ++r;

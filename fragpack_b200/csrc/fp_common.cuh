@@ -40,9 +40,10 @@ constexpr int kEscOrdinalCap = 4000;
 constexpr int kEscPad = 16;
 constexpr int kEscBytes = kEscPad + 64 * 7 + 4 * (kEscOrdinalCap + 8) + 32;  // 16528
 
-// Multipliers that are only known at run time, so that shifts and adds written
-// as integer multiply-adds stay on the multiply pipe instead of the (half-rate,
-// saturated) ALU pipe: x >> 16 = hi(x * 2^16), x >> 1 = hi(x * 2^31).
+// Multipliers that are only known at run time, so that adds written as integer
+// multiply-adds issue on the multiply pipe instead of the half-rate ALU pipe.
+// (Right shifts as high multiplies were measured and dropped: they cost two
+// dispatch slots each.)
 struct PipeConsts {
   uint32_t one, four, two16, two29, two30, two31;
 };
@@ -78,12 +79,17 @@ __device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
   return r;
 }
 
-__device__ __forceinline__ int warp_exclusive_sum(int v, int lane) {
+// Exclusive prefix sum over the warp.  shfl.up reports whether the source lane
+// exists, so each step is one shuffle and one predicated add.
+__device__ __forceinline__ int warp_exclusive_sum(int v, int /*lane*/) {
   int inc = v;
 #pragma unroll
   for (int d = 1; d < 32; d <<= 1) {
-    const int up = __shfl_up_sync(0xffffffffu, inc, d);
-    if (lane >= d) inc += up;
+    asm("{\n\t.reg .pred p;\n\t.reg .s32 t;\n\t"
+        "shfl.sync.up.b32 t|p, %0, %1, 0, 0xffffffff;\n\t"
+        "@p add.s32 %0, %0, t;\n\t}"
+        : "+r"(inc)
+        : "r"(d));
   }
   return inc - v;
 }
@@ -131,12 +137,11 @@ __device__ __forceinline__ void raw_record_words(const uint8_t* rec, int tid, Em
 // for st = 0..7 where w[0..3] are the BF16 pairs (j0 f0, j0 f1, j1 f0, j1 f1).
 //
 // `rec` may be shared or global memory.  `esc` is a kEscBytes scratch in
-// shared memory.  Within one record each warp touches only its own part of it,
+// shared memory.  `released()` is called after the last read of `rec` by this
+// warp.  Within one record each warp touches only its own part of `esc`,
 // so only warp-level synchronisation happens in here; but the parts move with
 // the record's escape prefixes, so two records may share one scratch only if a
-// block-wide barrier separates their decodes.  `released()` is called once every read of
-// `rec` by this warp has been made (dense part held in registers, escapes
-// expanded), so the caller may hand the record's buffer back to a producer.
+// block-wide barrier separates their decodes.
 //
 // Phases: (1) the warp expands its escape nibbles through the extended table
 // into sliding windows and patches raw scalars; (2) every owner counts its
@@ -146,14 +151,12 @@ __device__ __forceinline__ void raw_record_words(const uint8_t* rec, int tid, Em
 // The scheme is the one the format was laid out for
 // (fragpack/ops/fragpack_common.cuh:92-186).
 template <typename Released, typename Emit>
-__device__ __forceinline__ void coded_record_words(const uint8_t* rec, const HeadTables& tab,
-                                                   uint8_t* esc, int tid, const PipeConsts& k,
-                                                   Released&& released, Emit&& emit) {
+__device__ __forceinline__ void coded_record_words(const uint8_t* rec, int vlen,
+                                                   const HeadTables& tab, uint8_t* esc, int tid,
+                                                   const PipeConsts& k, Released&& released,
+                                                   Emit&& emit) {
   const int lane = tid & 31, warp = tid >> 5;
-  uint4 low[4];
   uint2 sym[3];
-#pragma unroll
-  for (int j = 0; j < 4; ++j) low[j] = reinterpret_cast<const uint4*>(rec)[j * kOwners + tid];
 #pragma unroll
   for (int m = 0; m < 3; ++m)
     sym[m] = reinterpret_cast<const uint2*>(rec + kLowBytes)[m * kOwners + tid];
@@ -166,40 +169,51 @@ __device__ __forceinline__ void coded_record_words(const uint8_t* rec, const Hea
   {
     const int end_esc = min(warp < 7 ? (int)h16[9 + warp] : (int)h32[0], kEscOrdinalCap);
     const uint32_t* nibbles = reinterpret_cast<const uint32_t*>(var + kHeaderBytes);
+    // Last nibble word inside the record: lanes past the warp's range clamp to it.
+    const int last_word = max(0, (vlen - kHeaderBytes - 4) >> 2);
     const uint4 ext = tab.ext;
     __syncwarp();  // the previous record's readers of `mine` are done
-    for (int g8 = (first_esc >> 3) + lane; 8 * g8 < end_esc; g8 += 32) {
-      const uint32_t n0 = nibbles[g8], n1 = nibbles[g8 + 1];
-      const uint32_t b0 = extended_bytes(ext, n0), b1 = extended_bytes(ext, mul_hi(n0, k.two16));
-      const uint32_t b2 = extended_bytes(ext, n1);
-      uint4* dst = reinterpret_cast<uint4*>(mine + 32 * g8);
-      dst[0] = make_uint4(b0, __funnelshift_r(b0, b1, 8), __funnelshift_r(b0, b1, 16),
-                          __funnelshift_r(b0, b1, 24));
-      dst[1] = make_uint4(b1, __funnelshift_r(b1, b2, 8), __funnelshift_r(b1, b2, 16),
-                          __funnelshift_r(b1, b2, 24));
+    // 31 groups of eight escapes per round: lane L expands group g8 and takes
+    // the first bytes of the next group from lane L + 1 (lane 31 only feeds).
+    for (int base = first_esc >> 3; 8 * base < end_esc; base += 31) {
+      const int g8 = base + lane;
+      const uint32_t n0 = nibbles[min(g8, last_word)];
+      const uint32_t b0 = extended_bytes(ext, n0), b1 = extended_bytes(ext, n0 >> 16);
+      const uint32_t b2 = __shfl_down_sync(0xffffffffu, b0, 1);
+      if (lane < 31 && 8 * g8 < end_esc) {
+        uint4* dst = reinterpret_cast<uint4*>(mine + 32 * g8);
+        dst[0] = make_uint4(b0, __funnelshift_r(b0, b1, 8), __funnelshift_r(b0, b1, 16),
+                            __funnelshift_r(b0, b1, 24));
+        dst[1] = make_uint4(b1, __funnelshift_r(b1, b2, 8), __funnelshift_r(b1, b2, 16),
+                            __funnelshift_r(b1, b2, 24));
+      }
     }
-    // At most kMaxWarpRaw raw scalars per warp: one patch per lane.
+    // Raw scalars are rare: at most kMaxWarpRaw per warp, one patch per lane.
     const int first_raw = h16[16 + warp];
     const int n_raw = min((warp < 7 ? (int)h16[17 + warp] : (int)h32[1]) - first_raw, kMaxWarpRaw);
-    uint32_t patch = 0;
-    if (lane < n_raw) {
-      // Clamped so that a malformed header cannot read past the variable region.
-      const uint32_t at = min(h32[2] + 4u * (uint32_t)(first_raw + lane), (uint32_t)(kVarCap - 4));
-      patch = *reinterpret_cast<const uint32_t*>(var + (at & ~3u));
-    }
-    __syncwarp();
-    released();
-    if (lane < n_raw) {
-      // The raw byte of ordinal x is byte j of window x - j.
-      const int x = min((int)(patch & 0xffffu), kEscOrdinalCap);
+    if (n_raw > 0) {  // uniform over the warp
+      uint32_t patch = 0;
+      if (lane < n_raw) {
+        // Clamped so that a malformed header cannot read past the variable region.
+        const uint32_t at =
+            min(h32[2] + 4u * (uint32_t)(first_raw + lane), (uint32_t)max(vlen - 4, 0));
+        patch = *reinterpret_cast<const uint32_t*>(var + (at & ~3u));
+      }
+      __syncwarp();
+      if (lane < n_raw) {
+        // The raw byte of ordinal x is byte j of window x - j.
+        const int x = min((int)(patch & 0xffffu), kEscOrdinalCap);
 #pragma unroll
-      for (int j = 0; j < 4; ++j) mine[4 * (x - j) + j] = (uint8_t)(patch >> 16);
+        for (int j = 0; j < 4; ++j) mine[4 * (x - j) + j] = (uint8_t)(patch >> 16);
+      }
+    } else {
+      __syncwarp();
     }
   }
 
   // Selector words (3-bit codes, bit 3 clear) of the eight words; escapes are
-  // the nibbles equal to 7.
-  uint32_t sel[8];
+  // the nibbles equal to 7, flagged in bit 3 of `flag`.
+  uint32_t sel[8], flag[8];
 #pragma unroll
   for (int gi = 0; gi < 2; ++gi) {
     const uint32_t w0 = gi == 0 ? sym[0].x : sym[1].y;
@@ -209,18 +223,18 @@ __device__ __forceinline__ void coded_record_words(const uint8_t* rec, const Hea
     sel[4 * gi + 1] = w1 & 0x77777777u;
     sel[4 * gi + 2] = w2 & 0x77777777u;
     // Bit 3 of the three stored words carries the fourth word, one bit each.
-    sel[4 * gi + 3] = (mul_hi(w0, k.two29) & 0x11111111u) | (mul_hi(w1, k.two30) & 0x22222222u) |
-                      (mul_hi(w2, k.two31) & 0x44444444u);
+    sel[4 * gi + 3] =
+        ((w0 >> 3) & 0x11111111u) | ((w1 >> 2) & 0x22222222u) | ((w2 >> 1) & 0x44444444u);
   }
   int count = 0;
 #pragma unroll
   for (int gi = 0; gi < 2; ++gi) {
+#pragma unroll
+    for (int x = 0; x < 4; ++x)
+      flag[4 * gi + x] = mad_lo(sel[4 * gi + x], k.one, 0x11111111u) & 0x88888888u;
     // The flags of four words sit on distinct bits once shifted by 0..3.
-    const uint32_t f0 = mad_lo(sel[4 * gi + 0], k.one, 0x11111111u) & 0x88888888u;
-    const uint32_t f1 = mad_lo(sel[4 * gi + 1], k.one, 0x11111111u) & 0x88888888u;
-    const uint32_t f2 = mad_lo(sel[4 * gi + 2], k.one, 0x11111111u) & 0x88888888u;
-    const uint32_t f3 = mad_lo(sel[4 * gi + 3], k.one, 0x11111111u) & 0x88888888u;
-    count += __popc(f0 | mul_hi(f1, k.two31) | mul_hi(f2, k.two30) | mul_hi(f3, k.two29));
+    count += __popc(flag[4 * gi] | (flag[4 * gi + 1] >> 1) | (flag[4 * gi + 2] >> 2) |
+                    (flag[4 * gi + 3] >> 3));
   }
   // A thread consumes at most 64 escapes: clamping its first ordinal bounds
   // every window read below.
@@ -228,31 +242,37 @@ __device__ __forceinline__ void coded_record_words(const uint8_t* rec, const Hea
   __syncwarp();  // expansion and patches visible to the whole warp
 
   uint32_t window = smem_addr(mine) + 4u * (uint32_t)ordinal;
+  uint4 lw;
 #pragma unroll
   for (int st = 0; st < 8; ++st) {
-    const uint32_t s = sel[st];
-    const uint32_t f = mad_lo(s, k.one, 0x11111111u) & 0x88888888u;
+    const uint32_t s = sel[st], f = flag[st];
     uint32_t ha = prmt(tab.p0, tab.p1, s);
-    uint32_t hb = prmt(tab.p0, tab.p1, mul_hi(s, k.two16));
-    uint32_t e0, e1;
-    asm("ld.shared.u32 %0, [%2];\n\tld.shared.u32 %1, [%2+16];"
-        : "=r"(e0), "=r"(e1)
-        : "r"(window)
-        : "memory");
-    window = mad_lo((uint32_t)__popc(f), k.four, window);
+    uint32_t hb = prmt(tab.p0, tab.p1, s >> 16);
+    // The next eight escape bytes are windows x and x + 4; the second one is
+    // only fetched by the (rare) owners with more than four escapes in this word.
+    const uint32_t n_here = (uint32_t)__popc(f);
+    uint32_t e0, e1 = 0;
+    asm("ld.shared.u32 %0, [%1];" : "=r"(e0) : "r"(window) : "memory");
+    if (n_here > 4) asm("ld.shared.u32 %0, [%1+16];" : "=r"(e1) : "r"(window) : "memory");
+    window = mad_lo(n_here, k.four, window);
     // Nibble n of `rank` = escapes among the nibbles below n.
     const uint32_t rank = f * 0x02222222u;
     // Selector nibble n: n keeps the table byte, 4 + n takes the escape byte.
-    const uint32_t pick = mad_hi(f, k.two31, 0x32103210u);
+    const uint32_t pick = (f >> 1) + 0x32103210u;
     ha = prmt(ha, prmt(e0, e1, rank), pick);
-    hb = prmt(hb, prmt(e0, e1, mul_hi(rank, k.two16)), mul_hi(pick, k.two16));
-    const uint4& lw = low[st >> 1];
+    hb = prmt(hb, prmt(e0, e1, rank >> 16), pick >> 16);
+    // Low bytes are fetched as they are needed (two words per 16-byte chunk):
+    // holding all sixteen registers across the loop cost more in lost
+    // instruction-level parallelism than the later release of the record costs.
+    if ((st & 1) == 0) lw = reinterpret_cast<const uint4*>(rec)[(st >> 1) * kOwners + tid];
     const uint32_t la = (st & 1) ? lw.z : lw.x;
     const uint32_t lb = (st & 1) ? lw.w : lw.y;
     const uint32_t w[4] = {__byte_perm(la, ha, 0x5140), __byte_perm(la, ha, 0x7362),
                            __byte_perm(lb, hb, 0x5140), __byte_perm(lb, hb, 0x7362)};
     emit(st, w);
   }
+  __syncwarp();
+  released();
 }
 
 // One owner's view of where its word scalars live in a token-major tile.
