@@ -78,18 +78,21 @@ struct DecodeParams {
   float* opart;
   float* ml;
   int32_t* status;
+  __nv_bfloat16* out;
   int64_t q_stride;   // in 32-bit words
   int64_t bt_stride;  // in entries
-  int kvh, group, units;
+  int64_t out_stride;  // in elements
+  int kvh, group, units, batch;
   float scale_log2;
   PipeConsts k;
 };
 
-// Plan (int32): [0] pages per chunk, [1] units in use, [2 + 2u] sequence and
-// [3 + 2u] first page of unit u (sequence -1: idle), [2 + 2 units + 2 b] first
-// unit and [.. + 1] chunk count of sequence b, then one spare word and the
-// status word.
-__host__ __device__ __forceinline__ int64_t plan_words(int units) { return 2 + 4LL * units + 2; }
+// Plan (int32, 16-byte aligned):
+//   [0] pages per chunk   [1] units in use   [2] status word   [3] spare
+//   [4 + 4u ..]      unit u: {sequence (-1: idle), first page, pages, sequence length}
+//   [4 + 4U + 2b ..] sequence b: {first unit, chunks}
+constexpr int kPlanStatus = 2;
+__host__ __device__ __forceinline__ int64_t plan_words(int units) { return 4 + 6LL * units; }
 
 // ---------------------------------------------------------------------------
 // mbarrier / bulk-copy helpers
@@ -188,13 +191,13 @@ struct Item {
 __device__ __forceinline__ bool load_item(const DecodeParams& p, int item, Item& it) {
   it.unit = item / p.kvh;
   it.head = item - it.unit * p.kvh;
-  it.seq_index = p.plan[2 + 2 * it.unit];
-  if (it.seq_index < 0) return false;
-  it.first_page = p.plan[3 + 2 * it.unit];
-  it.seq_len = p.seq_lens[it.seq_index];
-  const int total = (it.seq_len + 127) >> 7;
-  it.pages = max(0, min(total, it.first_page + p.plan[0]) - it.first_page);
-  return it.pages > 0;
+  // One 16-byte load: the planner stored everything an item needs.
+  const int4 u = reinterpret_cast<const int4*>(p.plan + 4)[it.unit];
+  it.seq_index = u.x;
+  it.first_page = u.y;
+  it.pages = u.z;
+  it.seq_len = u.w;
+  return it.seq_index >= 0 && it.pages > 0;
 }
 
 // ---------------------------------------------------------------------------
@@ -439,11 +442,10 @@ __device__ __forceinline__ void consume(const DecodeParams& p, Smem& sm) {
       float sum = 0.f;
 #pragma unroll
       for (int w = 0; w < kConsumerWarps; ++w) sum += sm.lsum[w][tid];
-      p.ml[(row0 + tid) * 2] = sm.mrow[tid];
-      p.ml[(row0 + tid) * 2 + 1] = sum;
+      *reinterpret_cast<float2*>(p.ml + (row0 + tid) * 2) = make_float2(sm.mrow[tid], sum);
     }
-    // The next item's first page barrier orders these reads before the next
-    // writes of lsum / mrow.
+    // The barriers of the next item order these reads of lsum / mrow before
+    // their next writes.
   }
 }
 
@@ -475,28 +477,44 @@ __global__ void __launch_bounds__(kThreads, 2) decode_attn_kernel(DecodeParams p
   }
 }
 
-// Merges the chunk partials of every sequence into BF16 out[B, H * group, 128].
-// Rows without context (CUDA-graph padding) become zeros.
-__global__ void __launch_bounds__(128)
+// Merges the chunk partials of every sequence into BF16 out[B, H * group, 128]:
+// grid (B, H), one warp per query head, four dims per lane.  Rows without
+// context (CUDA-graph padding) become zeros.  A separate launch on purpose:
+// merging inside the attention kernel needs a device-wide fence per item, which
+// was measured to cost several microseconds each under load.
+__global__ void __launch_bounds__(256)
 combine_kernel(const float* opart, const float* ml, const int32_t* plan, __nv_bfloat16* out,
                int64_t out_stride, int units, int group) {
-  const int b = blockIdx.x, d = threadIdx.x;
-  const int head = blockIdx.y / group, gq = blockIdx.y % group;
-  const int first = plan[2 + 2 * units + 2 * b], chunks = plan[3 + 2 * units + 2 * b];
-  const int64_t base = (int64_t)head * units + first;
+  const int b = blockIdx.x, kv_head = blockIdx.y;
+  const int head = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (head >= group) return;
+  const int2 seq = *reinterpret_cast<const int2*>(plan + 4 + 4 * units + 2 * b);
+  const int first = seq.x, chunks = seq.y;
+  const int64_t base = ((int64_t)kv_head * units + first) * 8 + head;
   float top = -INFINITY;
-  for (int s = 0; s < chunks; ++s) top = fmaxf(top, ml[((base + s) * 8 + gq) * 2]);
-  float den = 0.f, acc = 0.f;
+  for (int s = lane; s < chunks; s += 32) top = fmaxf(top, ml[(base + 8LL * s) * 2]);
+#pragma unroll
+  for (int x = 16; x; x >>= 1) top = fmaxf(top, __shfl_xor_sync(0xffffffffu, top, x));
+  float den = 0.f;
+  float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
   if (top != -INFINITY) {
     for (int s = 0; s < chunks; ++s) {
-      const int64_t row = (base + s) * 8 + gq;
-      const float w = exp2f(ml[row * 2] - top);
-      den += w * ml[row * 2 + 1];
-      acc += w * opart[row * 128 + d];
+      const int64_t row = base + 8LL * s;
+      const float2 mlv = *reinterpret_cast<const float2*>(ml + row * 2);
+      const float wgt = exp2f(mlv.x - top);
+      den += wgt * mlv.y;
+      const float4 part = reinterpret_cast<const float4*>(opart + row * 128)[lane];
+      acc.x += wgt * part.x;
+      acc.y += wgt * part.y;
+      acc.z += wgt * part.z;
+      acc.w += wgt * part.w;
     }
   }
-  out[(int64_t)b * out_stride + (int64_t)blockIdx.y * 128 + d] =
-      __float2bfloat16(den > 0.f ? acc / den : 0.f);
+  const float inv = den > 0.f ? 1.f / den : 0.f;
+  __nv_bfloat162* dst = reinterpret_cast<__nv_bfloat162*>(
+      out + (int64_t)b * out_stride + ((int64_t)kv_head * group + head) * 128 + 4 * lane);
+  dst[0] = __floats2bfloat162_rn(acc.x * inv, acc.y * inv);
+  dst[1] = __floats2bfloat162_rn(acc.z * inv, acc.w * inv);
 }
 
 // ---------------------------------------------------------------------------
@@ -572,11 +590,14 @@ plan_kernel(const int32_t* seq_lens, int32_t* plan, int batch, int units, int kv
   __syncthreads();
   const int ppc = (int)(0xfffff - (best & 0xfffff));
 
-  int32_t* seq_plan = plan + 2 + 2 * units;
+  int4* unit_tab = reinterpret_cast<int4*>(plan + 4);
+  int32_t* seq_plan = plan + 4 + 4 * units;
   int used = 0;
   for (int base = 0; base < batch; base += kPlanThreads) {
     const int b = base + tid;
-    const int chunks = b < batch ? (((seq_lens[b] + 127) >> 7) + ppc - 1) / ppc : 0;
+    const int len = b < batch ? seq_lens[b] : 0;
+    const int n_pages = (len + 127) >> 7;
+    const int chunks = (n_pages + ppc - 1) / ppc;
     const int before = warp_exclusive_sum(chunks, lane);
     if (lane == 31) warp_total[warp] = before + chunks;
     __syncthreads();
@@ -589,20 +610,18 @@ plan_kernel(const int32_t* seq_lens, int32_t* plan, int batch, int units, int kv
     if (b < batch) {
       seq_plan[2 * b] = first;
       seq_plan[2 * b + 1] = chunks;
-      for (int s = 0; s < chunks; ++s) {
-        plan[2 + 2 * (first + s)] = b;
-        plan[3 + 2 * (first + s)] = s * ppc;
-      }
+      for (int s = 0; s < chunks; ++s)
+        unit_tab[first + s] = make_int4(b, s * ppc, min(ppc, n_pages - s * ppc), len);
     }
     used += tile;
     __syncthreads();
   }
-  for (int u = used + tid; u < units; u += kPlanThreads) plan[2 + 2 * u] = -1;
+  for (int u = used + tid; u < units; u += kPlanThreads) unit_tab[u] = make_int4(-1, 0, 0, 0);
   if (tid == 0) {
     plan[0] = ppc;
     plan[1] = used;
-    plan[plan_words(units) - 2] = 0;
-    plan[plan_words(units) - 1] = 0;  // status
+    plan[kPlanStatus] = 0;
+    plan[3] = 0;
   }
 }
 
@@ -659,6 +678,11 @@ int fp_fused_decode(const void* q, int64_t q_stride, const int64_t* rec_addr,
              "decode workspace too small");
   FP_REQUIRE(plan_elems >= plan_words(units), "decode plan must hold %lld int32",
              (long long)plan_words(units));
+  FP_REQUIRE(reinterpret_cast<uintptr_t>(plan) % 16 == 0 && reinterpret_cast<uintptr_t>(opart) % 16 == 0 &&
+                 reinterpret_cast<uintptr_t>(ml) % 8 == 0,
+             "decode workspace must be 16-byte aligned");
+  FP_REQUIRE(out_stride % 2 == 0 && reinterpret_cast<uintptr_t>(out) % 4 == 0,
+             "out rows must be 4-byte aligned");
   const int sms = num_sms > 0 ? num_sms : device_sms();
   const int slots = 2 * sms;
   cudaStream_t st = (cudaStream_t)stream;
@@ -677,7 +701,10 @@ int fp_fused_decode(const void* q, int64_t q_stride, const int64_t* rec_addr,
   p.plan = plan;
   p.opart = opart;
   p.ml = ml;
-  p.status = plan + plan_words(units) - 1;
+  p.status = plan + kPlanStatus;
+  p.out = static_cast<__nv_bfloat16*>(out);
+  p.out_stride = out_stride;
+  p.batch = batch;
   p.q_stride = q_stride / 2;
   p.bt_stride = bt_stride;
   p.kvh = kv_heads;
@@ -694,8 +721,8 @@ int fp_fused_decode(const void* q, int64_t q_stride, const int64_t* rec_addr,
   const int grid = (int)(max_items < slots ? max_items : slots);
   decode_attn_kernel<<<grid, kThreads, smem, st>>>(p);
   FP_LAUNCH_CHECK("decode_attn_kernel");
-  combine_kernel<<<dim3(batch, kv_heads * group), 128, 0, st>>>(
-      opart, ml, plan, static_cast<__nv_bfloat16*>(out), out_stride, units, group);
+  combine_kernel<<<dim3(batch, kv_heads), 256, 0, st>>>(opart, ml, plan, p.out, out_stride, units,
+                                                        group);
   FP_LAUNCH_CHECK("combine_kernel");
   return FP_OK;
 }
@@ -720,7 +747,8 @@ constexpr int kStaticUnitHeads = 4096;  // largest kv_heads * units served
 constexpr int kStaticUnits = 4096;      // largest units served
 constexpr size_t kStaticOpartBytes = (size_t)kStaticUnitHeads * 8 * 128 * sizeof(float);
 constexpr size_t kStaticMlBytes = (size_t)kStaticUnitHeads * 8 * 2 * sizeof(float);
-constexpr size_t kStaticPlanBytes = ((2 + 4 * (size_t)kStaticUnits + 2) * sizeof(int32_t) + 255) / 256 * 256;
+constexpr size_t kStaticPlanBytes =
+    ((4 + 6 * (size_t)kStaticUnits) * sizeof(int32_t) + 255) / 256 * 256;
 constexpr size_t kStaticScratchBytes = kStaticOpartBytes + kStaticMlBytes + kStaticPlanBytes;
 
 // In host code this name is only a handle for cudaGetSymbolAddress; it is not
