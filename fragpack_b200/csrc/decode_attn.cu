@@ -18,6 +18,9 @@
 //  * one consumer barrier per page: probabilities are formed against the
 //    running maximum, and only a page that raises some head's maximum takes a
 //    second barrier to rescale.
+// The page loop is issue-bound and sits at the register limit of two CTAs per
+// SM; its speed moves by 5-10 % with small changes around it, so changes here
+// are re-measured on the steady-state case before they are kept.
 // Every device-side wait is bounded: when it runs out the CTA sets
 // FP_DECODE_WAIT_TIMEOUT in the status word, stops waiting and finishes its
 // control flow, so the context stays usable.
@@ -78,21 +81,18 @@ struct DecodeParams {
   float* opart;
   float* ml;
   int32_t* status;
-  __nv_bfloat16* out;
   int64_t q_stride;   // in 32-bit words
   int64_t bt_stride;  // in entries
-  int64_t out_stride;  // in elements
-  int kvh, group, units, batch;
+  int kvh, group, units;
   float scale_log2;
   PipeConsts k;
 };
 
-// Plan (int32, 16-byte aligned):
-//   [0] pages per chunk   [1] units in use   [2] status word   [3] spare
-//   [4 + 4u ..]      unit u: {sequence (-1: idle), first page, pages, sequence length}
-//   [4 + 4U + 2b ..] sequence b: {first unit, chunks}
-constexpr int kPlanStatus = 2;
-__host__ __device__ __forceinline__ int64_t plan_words(int units) { return 4 + 6LL * units; }
+// Plan (int32): [0] pages per chunk, [1] units in use, [2 + 2u] sequence and
+// [3 + 2u] first page of unit u (sequence -1: idle), [2 + 2 units + 2 b] first
+// unit and [.. + 1] chunk count of sequence b, then one spare word and the
+// status word.
+__host__ __device__ __forceinline__ int64_t plan_words(int units) { return 2 + 4LL * units + 2; }
 
 // ---------------------------------------------------------------------------
 // mbarrier / bulk-copy helpers
@@ -191,13 +191,13 @@ struct Item {
 __device__ __forceinline__ bool load_item(const DecodeParams& p, int item, Item& it) {
   it.unit = item / p.kvh;
   it.head = item - it.unit * p.kvh;
-  // One 16-byte load: the planner stored everything an item needs.
-  const int4 u = reinterpret_cast<const int4*>(p.plan + 4)[it.unit];
-  it.seq_index = u.x;
-  it.first_page = u.y;
-  it.pages = u.z;
-  it.seq_len = u.w;
-  return it.seq_index >= 0 && it.pages > 0;
+  it.seq_index = p.plan[2 + 2 * it.unit];
+  if (it.seq_index < 0) return false;
+  it.first_page = p.plan[3 + 2 * it.unit];
+  it.seq_len = p.seq_lens[it.seq_index];
+  const int total = (it.seq_len + 127) >> 7;
+  it.pages = max(0, min(total, it.first_page + p.plan[0]) - it.first_page);
+  return it.pages > 0;
 }
 
 // ---------------------------------------------------------------------------
@@ -442,10 +442,11 @@ __device__ __forceinline__ void consume(const DecodeParams& p, Smem& sm) {
       float sum = 0.f;
 #pragma unroll
       for (int w = 0; w < kConsumerWarps; ++w) sum += sm.lsum[w][tid];
-      *reinterpret_cast<float2*>(p.ml + (row0 + tid) * 2) = make_float2(sm.mrow[tid], sum);
+      p.ml[(row0 + tid) * 2] = sm.mrow[tid];
+      p.ml[(row0 + tid) * 2 + 1] = sum;
     }
-    // The barriers of the next item order these reads of lsum / mrow before
-    // their next writes.
+    // The next item's first page barrier orders these reads before the next
+    // writes of lsum / mrow.
   }
 }
 
@@ -488,7 +489,7 @@ combine_kernel(const float* opart, const float* ml, const int32_t* plan, __nv_bf
   const int b = blockIdx.x, kv_head = blockIdx.y;
   const int head = threadIdx.x >> 5, lane = threadIdx.x & 31;
   if (head >= group) return;
-  const int2 seq = *reinterpret_cast<const int2*>(plan + 4 + 4 * units + 2 * b);
+  const int2 seq = *reinterpret_cast<const int2*>(plan + 2 + 2 * units + 2 * b);
   const int first = seq.x, chunks = seq.y;
   const int64_t base = ((int64_t)kv_head * units + first) * 8 + head;
   float top = -INFINITY;
@@ -590,14 +591,11 @@ plan_kernel(const int32_t* seq_lens, int32_t* plan, int batch, int units, int kv
   __syncthreads();
   const int ppc = (int)(0xfffff - (best & 0xfffff));
 
-  int4* unit_tab = reinterpret_cast<int4*>(plan + 4);
-  int32_t* seq_plan = plan + 4 + 4 * units;
+  int32_t* seq_plan = plan + 2 + 2 * units;
   int used = 0;
   for (int base = 0; base < batch; base += kPlanThreads) {
     const int b = base + tid;
-    const int len = b < batch ? seq_lens[b] : 0;
-    const int n_pages = (len + 127) >> 7;
-    const int chunks = (n_pages + ppc - 1) / ppc;
+    const int chunks = b < batch ? (((seq_lens[b] + 127) >> 7) + ppc - 1) / ppc : 0;
     const int before = warp_exclusive_sum(chunks, lane);
     if (lane == 31) warp_total[warp] = before + chunks;
     __syncthreads();
@@ -610,18 +608,20 @@ plan_kernel(const int32_t* seq_lens, int32_t* plan, int batch, int units, int kv
     if (b < batch) {
       seq_plan[2 * b] = first;
       seq_plan[2 * b + 1] = chunks;
-      for (int s = 0; s < chunks; ++s)
-        unit_tab[first + s] = make_int4(b, s * ppc, min(ppc, n_pages - s * ppc), len);
+      for (int s = 0; s < chunks; ++s) {
+        plan[2 + 2 * (first + s)] = b;
+        plan[3 + 2 * (first + s)] = s * ppc;
+      }
     }
     used += tile;
     __syncthreads();
   }
-  for (int u = used + tid; u < units; u += kPlanThreads) unit_tab[u] = make_int4(-1, 0, 0, 0);
+  for (int u = used + tid; u < units; u += kPlanThreads) plan[2 + 2 * u] = -1;
   if (tid == 0) {
     plan[0] = ppc;
     plan[1] = used;
-    plan[kPlanStatus] = 0;
-    plan[3] = 0;
+    plan[plan_words(units) - 2] = 0;
+    plan[plan_words(units) - 1] = 0;  // status
   }
 }
 
@@ -678,7 +678,8 @@ int fp_fused_decode(const void* q, int64_t q_stride, const int64_t* rec_addr,
              "decode workspace too small");
   FP_REQUIRE(plan_elems >= plan_words(units), "decode plan must hold %lld int32",
              (long long)plan_words(units));
-  FP_REQUIRE(reinterpret_cast<uintptr_t>(plan) % 16 == 0 && reinterpret_cast<uintptr_t>(opart) % 16 == 0 &&
+  FP_REQUIRE(reinterpret_cast<uintptr_t>(plan) % 8 == 0 &&
+                 reinterpret_cast<uintptr_t>(opart) % 16 == 0 &&
                  reinterpret_cast<uintptr_t>(ml) % 8 == 0,
              "decode workspace must be 16-byte aligned");
   FP_REQUIRE(out_stride % 2 == 0 && reinterpret_cast<uintptr_t>(out) % 4 == 0,
@@ -701,10 +702,7 @@ int fp_fused_decode(const void* q, int64_t q_stride, const int64_t* rec_addr,
   p.plan = plan;
   p.opart = opart;
   p.ml = ml;
-  p.status = plan + kPlanStatus;
-  p.out = static_cast<__nv_bfloat16*>(out);
-  p.out_stride = out_stride;
-  p.batch = batch;
+  p.status = plan + plan_words(units) - 1;
   p.q_stride = q_stride / 2;
   p.bt_stride = bt_stride;
   p.kvh = kv_heads;
@@ -721,8 +719,8 @@ int fp_fused_decode(const void* q, int64_t q_stride, const int64_t* rec_addr,
   const int grid = (int)(max_items < slots ? max_items : slots);
   decode_attn_kernel<<<grid, kThreads, smem, st>>>(p);
   FP_LAUNCH_CHECK("decode_attn_kernel");
-  combine_kernel<<<dim3(batch, kv_heads), 256, 0, st>>>(opart, ml, plan, p.out, out_stride, units,
-                                                        group);
+  combine_kernel<<<dim3(batch, kv_heads), 256, 0, st>>>(
+      opart, ml, plan, static_cast<__nv_bfloat16*>(out), out_stride, units, group);
   FP_LAUNCH_CHECK("combine_kernel");
   return FP_OK;
 }
@@ -747,8 +745,7 @@ constexpr int kStaticUnitHeads = 4096;  // largest kv_heads * units served
 constexpr int kStaticUnits = 4096;      // largest units served
 constexpr size_t kStaticOpartBytes = (size_t)kStaticUnitHeads * 8 * 128 * sizeof(float);
 constexpr size_t kStaticMlBytes = (size_t)kStaticUnitHeads * 8 * 2 * sizeof(float);
-constexpr size_t kStaticPlanBytes =
-    ((4 + 6 * (size_t)kStaticUnits) * sizeof(int32_t) + 255) / 256 * 256;
+constexpr size_t kStaticPlanBytes = ((2 + 4 * (size_t)kStaticUnits + 2) * sizeof(int32_t) + 255) / 256 * 256;
 constexpr size_t kStaticScratchBytes = kStaticOpartBytes + kStaticMlBytes + kStaticPlanBytes;
 
 // In host code this name is only a handle for cudaGetSymbolAddress; it is not

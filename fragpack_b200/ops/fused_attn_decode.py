@@ -11,8 +11,8 @@ reference's tests and callers run unchanged.  Differences, all internal:
   are executed by persistent CTAs that stream every record of their items
   through one bulk-copy ring; :func:`decode_units` therefore reserves more
   split capacity than the reference (finer chunks cost almost nothing);
-* ``plan[2]`` is a status word that the kernel sets if a bounded device-side
-  wait ever runs out (:func:`decode_status`).
+* the ``plan`` workspace ends with a status word that the kernel sets if a
+  bounded device-side wait ever runs out (:func:`decode_status`).
 
 Records are located through ``rec_addr[P, 2, H]`` (absolute device addresses)
 and ``rec_len[P, 2, H]`` (record bytes minus ``DENSE_BYTES``; raw records
@@ -80,9 +80,8 @@ def decode_units(batch: int, kv_heads: int, num_sms: int) -> int:
 def workspace_elems(kv_heads: int, units: int) -> tuple[int, int, int]:
     """Return the element counts of the ``(opart, ml, plan)`` workspace.
 
-    Reference: ``fused_attn_decode.py:88-102``.  The plan is larger than the
-    reference's: four header words (one is the status word), four words per
-    unit and two per sequence.
+    Reference: ``fused_attn_decode.py:88-102``.  The plan holds two more words
+    than the reference's: a spare and the status word.
 
     Args:
         kv_heads: KV heads per sequence.
@@ -92,7 +91,7 @@ def workspace_elems(kv_heads: int, units: int) -> tuple[int, int, int]:
         Float elements of ``opart`` and ``ml``, int32 elements of ``plan``.
     """
     rows = kv_heads * units * GQA
-    return rows * 128, rows * 2, 4 + 6 * units
+    return rows * 128, rows * 2, 2 + 4 * units + 2
 
 
 @functools.cache
@@ -172,7 +171,7 @@ def decode_status(workspace: tuple[torch.Tensor, torch.Tensor, torch.Tensor], un
         0, or a combination of ``DECODE_*`` bits: the kernel gave up a bounded
         wait and the outputs of that step are invalid.
     """
-    return int(workspace[2][2].item())
+    return int(workspace[2][2 + 4 * units + 1].item())
 
 
 __all__ = [
