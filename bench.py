@@ -476,6 +476,97 @@ def run_ours(args) -> dict:
     return line if rank == 0 else {}
 
 
+def run_codec(args) -> dict:
+    """Prefill side (configuration 4): token write + block encode, then decompression.
+
+    One step = one layer of the MHA stress geometry (32 KV heads, 16 x 8192
+    tokens = 1024 blocks): the tokens are scattered into staging, every completed
+    block is encoded into its arena page, and all blocks are decompressed into the
+    BF16 workspace.  Each phase is timed with CUDA events on its own.
+    """
+    from fragpack_b200 import synth
+    from fragpack_b200.compression.attn_tables import device_tables
+    from fragpack_b200.ops.hbm_kv import HbmKvStore, page_bytes
+
+    torch.cuda.set_device(0)
+    device = torch.device("cuda", 0)
+    cfg = workloads.CONFIGS["c4"]
+    junk = args.junk if args.junk >= 0 else 0.009
+    heads, layers = cfg.kv_heads, args.layers or 2
+    tokens = (args.batch or cfg.batch) * (args.ctx or cfg.ctx_max)
+    blocks = tokens // 128
+    scales = synth.channel_scales(args.seed + 1, layers, heads)
+    gen = torch.Generator(device=device).manual_seed(args.seed + 4)
+    scales_dev = torch.from_numpy(scales).to(device)
+    table = np.stack([workloads.calibrate_on_device(gen, scales_dev[layer], 0.0, junk)
+                      for layer in range(layers)])
+    arenas = [torch.empty((blocks + 1, page_bytes(heads)), dtype=torch.uint8, device=device)
+              for _ in range(layers)]
+    store = HbmKvStore(arenas, heads, device_tables(table, device), max_tokens=tokens,
+                       staging_slots=1, overflow_records=args.overflow)
+    ids = torch.from_numpy(np.random.default_rng(args.seed).permutation(np.arange(1, blocks + 1)))
+    slots = (ids.repeat_interleave(128) * 128 + torch.arange(128).repeat(blocks)).to(device)
+    ids_dev = ids.to(torch.int32).to(device)
+    wk = torch.empty(blocks, 128, heads, 128, dtype=torch.bfloat16, device=device)
+    wv = torch.empty_like(wk)
+    kv = [synth.kv_tokens_torch(gen, scales_dev[layer], tokens, 0.0, junk) for layer in range(layers)]
+    times = {"write": [], "encode": [], "gather": []}
+    ok = True
+    for it in range(max(args.warmup, 1) + args.steps):
+        store.prepare(slots, tokens, np.zeros(0, np.int32))
+        for layer in range(layers):
+            ev = [torch.cuda.Event(enable_timing=True) for _ in range(4)]
+            ev[0].record()
+            store.write(layer, kv[layer][0], kv[layer][1], slots)
+            ev[1].record()
+            store.encode(layer, blocks)
+            ev[2].record()
+            store.gather(layer, ids_dev, wk, wv)
+            ev[3].record()
+            torch.cuda.synchronize()
+            if it >= max(args.warmup, 1):
+                for name, a, b in (("write", 0, 1), ("encode", 1, 2), ("gather", 2, 3)):
+                    times[name].append(ev[a].elapsed_time(ev[b]))
+            if it == 0:
+                # Bit-exact reconstruction of what was written.
+                src_k = kv[layer][0].view(blocks, 128, heads, 128)
+                src_v = kv[layer][1].view(blocks, 128, heads, 128)
+                ok &= bool(torch.equal(wk, src_k)) and bool(torch.equal(wv, src_v))
+        store.commit()
+    counters = store.counters.cpu().numpy()
+    records = blocks * 2 * heads
+    rec_bytes = float((store.rec_len[0, ids_dev.long()].to(torch.int64) + ap.DENSE_BYTES).sum().item())
+    peak, peak_kind = measured_hbm_peak()
+    ms = {k: float(np.mean(v)) for k, v in times.items()}
+    enc_bytes = records * 32768 + rec_bytes
+    dec_bytes = rec_bytes + records * 32768
+    return {
+        "metric": "block_encode_and_decompress_throughput",
+        "value": enc_bytes / (ms["encode"] * 1e-3) / 1e9,
+        "unit": "GB/s (encode: raw bytes read + record bytes written)",
+        "n_gpus": 1,
+        "steps": args.steps,
+        "warmup": max(args.warmup, 1),
+        "ms_per_step": ms["write"] + ms["encode"] + ms["gather"],
+        "higher_is_better": True,
+        "config": {"workload": cfg.name, "layers_resident": layers, "kv_heads": heads,
+                   "tokens_per_layer": tokens, "blocks_per_layer": blocks, "junk_fraction": junk,
+                   "overflow_records": args.overflow},
+        "bit_exact_roundtrip": ok,
+        "mean_record_bytes": rec_bytes / records,
+        "counters": {"encoded": int(counters[7]), "fallbacks": int(counters[6]),
+                     "spills": int(counters[8]), "err_overflow": int(counters[5]),
+                     "err_staging": int(counters[4])},
+        "write": {"ms_per_layer": ms["write"],
+                  "GBps": (records * 32768 * 2) / (ms["write"] * 1e-3) / 1e9},
+        "encode": {"ms_per_layer": ms["encode"], "GBps": enc_bytes / (ms["encode"] * 1e-3) / 1e9,
+                   "roofline_frac": enc_bytes / (ms["encode"] * 1e-3) / 1e9 / peak},
+        "decompress": {"ms_per_layer": ms["gather"], "GBps": dec_bytes / (ms["gather"] * 1e-3) / 1e9,
+                       "roofline_frac": dec_bytes / (ms["gather"] * 1e-3) / 1e9 / peak},
+        "peak": peak, "peak_kind": peak_kind,
+    }
+
+
 def run_reference(args) -> dict:
     """Reference arm: the CPU codec (oracle port) + torch CPU fp32 attention."""
     rank = int(os.environ.get("RANK", "0"))
@@ -551,7 +642,9 @@ def main() -> None:
     parser.add_argument("--steps", type=int, default=20)
     parser.add_argument("--warmup", type=int, default=5)
     parser.add_argument("--impl", choices=("ours", "reference"), default="ours")
-    parser.add_argument("--workload", choices=("c2", "c3", "c5"), default=None)
+    parser.add_argument("--workload", choices=("c2", "c3", "c4", "c5"), default=None)
+    parser.add_argument("--junk", type=float, default=-1.0, help="c4: junk fraction (default 0.009)")
+    parser.add_argument("--overflow", type=int, default=8192, help="c4: overflow records")
     parser.add_argument("--layers", type=int, default=0, help="resident layers (default: what fits)")
     parser.add_argument("--hbm-budget-gb", type=float, default=40.0)
     parser.add_argument("--seed", type=int, default=0)
@@ -565,7 +658,10 @@ def main() -> None:
     parser.add_argument("--cpu-seqs", type=int, default=4)
     parser.add_argument("--cpu-pairs", type=int, default=8)
     args = parser.parse_args()
-    line = run_reference(args) if args.impl == "reference" else run_ours(args)
+    if args.workload == "c4" and args.impl == "ours":
+        line = run_codec(args)
+    else:
+        line = run_reference(args) if args.impl == "reference" else run_ours(args)
     if line:
         print(json.dumps(line))
 

@@ -462,6 +462,10 @@ __global__ void __launch_bounds__(kThreads, 2) decode_attn_kernel(DecodeParams p
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   __syncthreads();
+  // Prologue done (barriers initialised).  Under a programmatic dependent
+  // launch the preceding grid may still be running: wait for it before reading
+  // queries or KV, or writing partial results.
+  asm volatile("griddepcontrol.wait;" ::: "memory");
   if (threadIdx.x >= kConsumers) {
     produce(p, sm);
   } else {
@@ -482,12 +486,19 @@ __global__ void __launch_bounds__(kThreads, 2) decode_attn_kernel(DecodeParams p
 // grid (B, H), one warp per query head, four dims per lane.  Rows without
 // context (CUDA-graph padding) become zeros.  A separate launch on purpose:
 // merging inside the attention kernel needs a device-wide fence per item, which
-// was measured to cost several microseconds each under load.
+// was measured to cost several microseconds each under load.  The launch is
+// programmatically dependent on the attention kernel, so its blocks are already
+// resident (and past their index arithmetic) when the last partial lands.
 __global__ void __launch_bounds__(256)
 combine_kernel(const float* opart, const float* ml, const int32_t* plan, __nv_bfloat16* out,
                int64_t out_stride, int units, int group) {
   const int b = blockIdx.x, kv_head = blockIdx.y;
   const int head = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  // Let the next grid in the stream start its prologue now; it waits for this
+  // grid before it touches anything this grid reads or writes.
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  // Everything read below was written by earlier grids: wait for them.
+  asm volatile("griddepcontrol.wait;" ::: "memory");
   if (head >= group) return;
   const int2 seq = *reinterpret_cast<const int2*>(plan + 2 + 2 * units + 2 * b);
   const int first = seq.x, chunks = seq.y;
@@ -499,16 +510,25 @@ combine_kernel(const float* opart, const float* ml, const int32_t* plan, __nv_bf
   float den = 0.f;
   float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
   if (top != -INFINITY) {
-    for (int s = 0; s < chunks; ++s) {
-      const int64_t row = base + 8LL * s;
-      const float2 mlv = *reinterpret_cast<const float2*>(ml + row * 2);
-      const float wgt = exp2f(mlv.x - top);
-      den += wgt * mlv.y;
-      const float4 part = reinterpret_cast<const float4*>(opart + row * 128)[lane];
-      acc.x += wgt * part.x;
-      acc.y += wgt * part.y;
-      acc.z += wgt * part.z;
-      acc.w += wgt * part.w;
+    // Eight chunks per round, all loads issued before the first use.
+    for (int s0 = 0; s0 < chunks; s0 += 8) {
+      float2 mlv[8];
+      float4 part[8];
+#pragma unroll
+      for (int k = 0; k < 8; ++k) {
+        const int64_t row = base + 8LL * min(s0 + k, chunks - 1);
+        mlv[k] = *reinterpret_cast<const float2*>(ml + row * 2);
+        part[k] = reinterpret_cast<const float4*>(opart + row * 128)[lane];
+      }
+#pragma unroll
+      for (int k = 0; k < 8; ++k) {
+        const float wgt = s0 + k < chunks ? exp2f(mlv[k].x - top) : 0.f;
+        den += wgt * mlv[k].y;
+        acc.x += wgt * part[k].x;
+        acc.y += wgt * part[k].y;
+        acc.z += wgt * part[k].z;
+        acc.w += wgt * part[k].w;
+      }
     }
   }
   const float inv = den > 0.f ? 1.f / den : 0.f;
@@ -717,10 +737,42 @@ int fp_fused_decode(const void* q, int64_t q_stride, const int64_t* rec_addr,
     return rc;
   const long long max_items = (long long)units * kv_heads;
   const int grid = (int)(max_items < slots ? max_items : slots);
-  decode_attn_kernel<<<grid, kThreads, smem, st>>>(p);
-  FP_LAUNCH_CHECK("decode_attn_kernel");
-  combine_kernel<<<dim3(batch, kv_heads), 256, 0, st>>>(
-      opart, ml, plan, static_cast<__nv_bfloat16*>(out), out_stride, units, group);
+  {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(grid);
+    cfg.blockDim = dim3(kThreads);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    if (int rc = cuda_status(cudaLaunchKernelEx(&cfg, decode_attn_kernel, p), "decode_attn_kernel"))
+      return rc;
+  }
+  {
+    // Programmatic dependent launch: the merge may be scheduled while the
+    // attention grid drains; it waits for that grid inside the kernel.
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(batch, kv_heads);
+    cfg.blockDim = dim3(256);
+    cfg.dynamicSmemBytes = 0;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    const float* opart_c = opart;
+    const float* ml_c = ml;
+    const int32_t* plan_c = plan;
+    __nv_bfloat16* out_c = static_cast<__nv_bfloat16*>(out);
+    if (int rc = cuda_status(cudaLaunchKernelEx(&cfg, combine_kernel, opart_c, ml_c, plan_c, out_c,
+                                                out_stride, (int)units, (int)group),
+                             "combine_kernel"))
+      return rc;
+  }
   FP_LAUNCH_CHECK("combine_kernel");
   return FP_OK;
 }
