@@ -261,20 +261,44 @@ write_kernel(StoreView v, const uint16_t* key, const uint16_t* value, int64_t ks
 // ---------------------------------------------------------------------------
 struct EncodeShared {
   __align__(16) uint8_t var[kVarCap];
-  uint8_t rank[256];
+  // Per high byte: low nibble = 3-bit primary code (7 = escape), high nibble =
+  // escape nibble (rank - 7, or 15 for a byte outside the table).
+  __align__(16) uint8_t composite[256];
   int warp_sum[2][8];
   uint8_t* dst;
   int raw;
 };
+
+// Fills the composite table from `rank_of` (one entry per thread).
+__device__ __forceinline__ void load_composite(EncodeShared& sh, const uint8_t* rank_of, int tid) {
+  const uint32_t r = rank_of[tid];
+  const uint32_t code = min(r, (uint32_t)kPrimaryDirect);
+  const uint32_t nib = r < kPrimaryDirect ? 0u : (r < kTableEntries ? r - kPrimaryDirect : 15u);
+  sh.composite[tid] = (uint8_t)(code | (nib << 4));
+}
 
 struct EncodePlan {
   int var_len;   // variable-region bytes if coded
   bool codes;    // false: raw fallback (attn_page.py:200-202)
 };
 
-// `place(plan)` runs on thread 0 only and returns where the record goes and
-// whether it must be stored raw (a coded record that no longer fits its page
-// is spilled raw); a null destination drops the record.
+// Composite bytes of the four high bytes packed in `hi`.
+__device__ __forceinline__ uint32_t composite4(const EncodeShared& sh, uint32_t hi) {
+  const uint32_t c0 = sh.composite[hi & 0xffu], c1 = sh.composite[(hi >> 8) & 0xffu];
+  const uint32_t c2 = sh.composite[(hi >> 16) & 0xffu], c3 = sh.composite[hi >> 24];
+  return c0 | (c1 << 8) | (c2 << 16) | (c3 << 24);
+}
+
+// Low nibbles of four bytes -> four adjacent nibbles (16 bits).
+__device__ __forceinline__ uint32_t low_nibbles(uint32_t c) {
+  uint32_t t = c & 0x0f0f0f0fu;
+  t = (t | (t >> 4)) & 0x00ff00ffu;
+  return (t | (t >> 8)) & 0xffffu;
+}
+
+// `place(plan, raw)` runs on thread 0 only and returns where the record goes;
+// it sets `raw` when the record must be stored raw (it does not code, or it
+// codes but no longer fits its page); a null destination drops the record.
 template <typename Place>
 __device__ __forceinline__ void encode_cta(const uint4 (&wd)[8], EncodeShared& sh, int tid,
                                            Place&& place) {
@@ -282,37 +306,44 @@ __device__ __forceinline__ void encode_cta(const uint4 (&wd)[8], EncodeShared& s
   for (int i = tid; i < kVarCap / 16; i += kOwners)
     reinterpret_cast<uint4*>(sh.var)[i] = make_uint4(0, 0, 0, 0);
 
-  // Classify the 64 scalars: 3-bit primary code into the symbol words, escape
-  // nibbles into a queue (first 16), escape and raw masks.
-  uint32_t sym[6] = {0, 0, 0, 0, 0, 0};
-  uint64_t esc_mask = 0, raw_mask = 0, queue = 0;
-  int n_esc = 0;
+  // Classify the 64 scalars four at a time: primary codes as nibble words,
+  // escape nibbles appended to a queue (first 16; longer runs are redone below).
+  uint32_t codes[8];
+  uint64_t queue = 0;
+  uint32_t raw_q[4] = {0, 0, 0, 0};  // first raw entries: local ordinal | high << 16
+  int n_esc = 0, n_raw = 0;
 #pragma unroll
   for (int st = 0; st < 8; ++st) {
     const uint32_t hi_a = __byte_perm(wd[st].x, wd[st].y, 0x7531);
     const uint32_t hi_b = __byte_perm(wd[st].z, wd[st].w, 0x7531);
+    const uint32_t ca = composite4(sh, hi_a), cb = composite4(sh, hi_b);
+    codes[st] = low_nibbles(ca) | (low_nibbles(cb) << 16);
+    uint32_t f = (codes[st] + 0x11111111u) & 0x88888888u;  // nibbles equal to 7
+    while (f) {
+      const int pos = (__ffs(f) - 1) >> 2;
+      f &= f - 1;
+      const int shift = 8 * (pos & 3);
+      const uint32_t nib = (((pos < 4) ? ca : cb) >> (shift + 4)) & 15u;
+      if (n_esc < 16) queue |= (uint64_t)nib << (4 * n_esc);
+      if (nib == 15u) {
+        const uint32_t entry = (uint32_t)n_esc | (((((pos < 4) ? hi_a : hi_b) >> shift) & 0xffu) << 16);
 #pragma unroll
-    for (int e = 0; e < 8; ++e) {
-      const int sc = 8 * st + e, gi = sc >> 5, sg = sc & 31;
-      const uint32_t high = ((e < 4 ? hi_a : hi_b) >> (8 * (e & 3))) & 0xffu;
-      const uint32_t r = sh.rank[high];
-      const uint32_t code = min(r, (uint32_t)kPrimaryDirect);
-      if (sg < 24) {
-        sym[3 * gi + (sg >> 3)] |= code << (4 * (sg & 7));
-      } else {
-#pragma unroll
-        for (int k = 0; k < 3; ++k) sym[3 * gi + k] |= ((code >> k) & 1u) << (4 * (sg - 24) + 3);
+        for (int x = 0; x < 4; ++x)
+          if (n_raw == x) raw_q[x] = entry;
+        ++n_raw;
       }
-      if (r >= kPrimaryDirect) {
-        const uint32_t nib = r < kTableEntries ? r - kPrimaryDirect : 15u;
-        if (n_esc < 16) queue |= (uint64_t)nib << (4 * n_esc);
-        ++n_esc;
-        esc_mask |= 1ull << sc;
-        if (r >= kTableEntries) raw_mask |= 1ull << sc;
-      }
+      ++n_esc;
     }
   }
-  const int n_raw = __popcll(raw_mask);
+  // Symbol words: per 32-scalar group three words; bit 3 of word k's nibble j
+  // is bit k of the code of scalar 24 + j (attn_page.py:174-181).
+  uint32_t sym[6];
+#pragma unroll
+  for (int gi = 0; gi < 2; ++gi)
+#pragma unroll
+    for (int k = 0; k < 3; ++k)
+      sym[3 * gi + k] = codes[4 * gi + k] | (((codes[4 * gi + 3] >> k) & 0x11111111u) << 3);
+
   const int esc_before = warp_exclusive_sum(n_esc, lane);
   const int raw_before = warp_exclusive_sum(n_raw, lane);
   if (lane == 31) {
@@ -336,22 +367,18 @@ __device__ __forceinline__ void encode_cta(const uint4 (&wd)[8], EncodeShared& s
   EncodePlan plan;
   plan.var_len = (raw_offset + 4 * raw_total + 15) & ~15;
   plan.codes = plan.var_len <= kVarCap && raw_worst <= kMaxWarpRaw;
+  // Thread 0 places the record (global atomics, several microseconds) while the
+  // block builds the variable region in shared memory; the destination is only
+  // needed for the final stores.
   if (tid == 0) {
     bool raw = !plan.codes;
     sh.dst = place(plan, raw);
     sh.raw = raw;
   }
-  __syncthreads();
-  uint8_t* dst = sh.dst;
-  if (dst == nullptr) return;
-  if (sh.raw) {
-#pragma unroll
-    for (int st = 0; st < 8; ++st) reinterpret_cast<uint4*>(dst)[st * kOwners + tid] = wd[st];
-    return;
-  }
-
   uint32_t* var32 = reinterpret_cast<uint32_t*>(sh.var);
-  if (n_esc > 0 && n_esc <= 16) {
+  if (!plan.codes) {
+    // nothing to build: the record is stored raw
+  } else if (n_esc > 0 && n_esc <= 16) {
     // This owner's nibbles are consecutive from nibble `esc_at` of the stream
     // that starts at byte 48 (word 12).
     const int word = (kHeaderBytes >> 2) + (esc_at >> 3), shift = 4 * (esc_at & 7);
@@ -361,26 +388,31 @@ __device__ __forceinline__ void encode_cta(const uint4 (&wd)[8], EncodeShared& s
     if ((uint32_t)(lo >> 32)) atomicOr(&var32[word + 1], (uint32_t)(lo >> 32));
     if (hi) atomicOr(&var32[word + 2], hi);
   }
-  if (n_esc > 16 || n_raw > 0) {
-    // Rare: long escape runs, and raw entries `ordinal | high << 16`.
+  if (plan.codes && n_raw > 0 && n_raw <= 4 && n_esc <= 16) {
+    // Raw entries `ordinal | high << 16` (attn_page.py:188-191) from the queue.
+#pragma unroll
+    for (int x = 0; x < 4; ++x)
+      if (x < n_raw) var32[(raw_offset >> 2) + raw_at + x] = raw_q[x] + (uint32_t)esc_at;
+  }
+  if (plan.codes && (n_esc > 16 || n_raw > 4)) {
+    // Rare: more escapes or raw scalars than the queues hold.  Walk the
+    // scalars again.
     int ordinal = esc_at;
 #pragma unroll
     for (int st = 0; st < 8; ++st) {
-      const uint32_t hi_a = __byte_perm(wd[st].x, wd[st].y, 0x7531);
-      const uint32_t hi_b = __byte_perm(wd[st].z, wd[st].w, 0x7531);
+      const uint32_t highs[2] = {__byte_perm(wd[st].x, wd[st].y, 0x7531),
+                                 __byte_perm(wd[st].z, wd[st].w, 0x7531)};
 #pragma unroll
       for (int e = 0; e < 8; ++e) {
-        const int sc = 8 * st + e;
-        if ((esc_mask >> sc) & 1ull) {
-          const uint32_t high = ((e < 4 ? hi_a : hi_b) >> (8 * (e & 3))) & 0xffu;
+        const uint32_t high = (highs[e >> 2] >> (8 * (e & 3))) & 0xffu;
+        const uint32_t c = sh.composite[high];
+        if ((c & 7u) == (uint32_t)kPrimaryDirect) {
+          const uint32_t nib = c >> 4;
           if (n_esc > 16) {
-            const uint32_t r = sh.rank[high];
-            const uint32_t nib = r < kTableEntries ? r - kPrimaryDirect : 15u;
             const int bit = 8 * kHeaderBytes + 4 * ordinal;
             atomicOr(&var32[bit >> 5], nib << (bit & 31));
           }
-          if ((raw_mask >> sc) & 1ull)
-            var32[(raw_offset >> 2) + raw_at++] = (uint32_t)ordinal | (high << 16);
+          if (nib == 15u) var32[(raw_offset >> 2) + raw_at++] = (uint32_t)ordinal | (high << 16);
           ++ordinal;
         }
       }
@@ -400,6 +432,14 @@ __device__ __forceinline__ void encode_cta(const uint4 (&wd)[8], EncodeShared& s
       r += sh.warp_sum[1][w];
     }
   }
+  __syncthreads();  // placement known, variable region complete
+  uint8_t* dst = sh.dst;
+  if (dst == nullptr) return;
+  if (sh.raw) {
+#pragma unroll
+    for (int st = 0; st < 8; ++st) reinterpret_cast<uint4*>(dst)[st * kOwners + tid] = wd[st];
+    return;
+  }
   // Dense part: low bytes in four 16-byte chunks, symbols in three 8-byte
   // chunks, both chunk-major (attn_page.py:272-276).
 #pragma unroll
@@ -413,14 +453,13 @@ __device__ __forceinline__ void encode_cta(const uint4 (&wd)[8], EncodeShared& s
   for (int m = 0; m < 3; ++m)
     reinterpret_cast<uint2*>(dst + kLowBytes)[m * kOwners + tid] =
         make_uint2(sym[2 * m], sym[2 * m + 1]);
-  __syncthreads();
   for (int i = tid; i < plan.var_len / 16; i += kOwners)
     reinterpret_cast<uint4*>(dst + kDenseBytes)[i] = reinterpret_cast<const uint4*>(sh.var)[i];
 }
 
 // grid (max_close, 2 H): CTA (i, rec) encodes record `rec` of close_list[i]
 // at `layer` from staging.  hbm_kv.cu:257-429.
-__global__ void __launch_bounds__(kOwners)
+__global__ void __launch_bounds__(kOwners, 3)
 encode_kernel(StoreView v, int layer, uint8_t* arena, int64_t page_bytes, const uint8_t* rank_of) {
   __shared__ EncodeShared sh;
   const fp_store& s = v.s;
@@ -429,7 +468,7 @@ encode_kernel(StoreView v, int layer, uint8_t* arena, int64_t page_bytes, const 
   const int block = s.close_list[blockIdx.x];
   uint8_t* src = v.staging(s.wslot[block], layer, rec);
   const int64_t idx = v.table_index(layer, block, rec);
-  sh.rank[tid] = rank_of[((int64_t)layer * 2 * s.H + rec) * 256 + tid];
+  load_composite(sh, rank_of + ((int64_t)layer * 2 * s.H + rec) * 256, tid);
   uint4 wd[8];
 #pragma unroll
   for (int st = 0; st < 8; ++st) wd[st] = reinterpret_cast<const uint4*>(src)[st * kOwners + tid];
@@ -448,22 +487,33 @@ encode_kernel(StoreView v, int layer, uint8_t* arena, int64_t page_bytes, const 
   encode_cta(wd, sh, tid, [&](const EncodePlan& plan, bool& raw) -> uint8_t* {
     int at = -1;
     if (plan.codes) {
-      // Claim page bytes with a CAS, so that a record too large for what is
-      // left does not block the block's smaller records.
+      // Claim page bytes.  Fast path: one fetch-add (the records of a page are
+      // encoded at the same time, and a compare-and-swap loop on one word
+      // serialises them with retries).  If that overshoots the page the add is
+      // undone and a compare-and-swap loop decides, so that a record too large
+      // for what is left does not block the block's smaller records.
       int32_t* fill = s.fill + (int64_t)layer * s.NB + block;
       const int need = kDenseBytes + plan.var_len;
-      int seen = *reinterpret_cast<volatile int32_t*>(fill);
-      while ((int64_t)seen + need <= page_bytes) {
-        const int before = atomicCAS(fill, seen, seen + need);
-        if (before == seen) {
-          at = seen;
-          break;
+      const int got = atomicAdd(fill, need);
+      if ((int64_t)got + need <= page_bytes) {
+        at = got;
+      } else {
+        atomicSub(fill, need);
+        int seen = *reinterpret_cast<volatile int32_t*>(fill);
+        while ((int64_t)seen + need <= page_bytes) {
+          const int before = atomicCAS(fill, seen, seen + need);
+          if (before == seen) {
+            at = seen;
+            break;
+          }
+          seen = before;
         }
-        seen = before;
       }
       if (at < 0) atomicAdd(&s.counters[FP_CTR_SPILLS], 1);
     }
-    atomicAdd(&s.counters[FP_CTR_ENCODED], 1);
+    // One add per closed block-layer (by its first record) instead of one per
+    // record: tens of thousands of adds to one address serialise in the L2.
+    if (rec == 0) atomicAdd(&s.counters[FP_CTR_ENCODED], 2 * s.H);
     if (at >= 0) {
       uint8_t* dst = arena + (int64_t)block * page_bytes + at;
       s.rec_addr[idx] = reinterpret_cast<int64_t>(dst);
@@ -546,7 +596,7 @@ __device__ __forceinline__ void word_to_tile(uint8_t* tile, int kv, const OwnerC
 constexpr int kTileBytes = 128 * 256;
 
 // Batch encoder over token-major records: grid = records.
-__global__ void __launch_bounds__(kOwners)
+__global__ void __launch_bounds__(kOwners, 3)
 encode_records_kernel(const uint8_t* raw, const uint8_t* rank_of, const int32_t* table_index,
                       const int32_t* kv, uint8_t* out, int64_t out_stride, int32_t* out_len) {
   extern __shared__ __align__(16) uint8_t dyn[];
@@ -555,7 +605,7 @@ encode_records_kernel(const uint8_t* raw, const uint8_t* rank_of, const int32_t*
   const int64_t i = blockIdx.x;
   const int tid = threadIdx.x;
   const int which = kv[i];
-  sh.rank[tid] = rank_of[(int64_t)(table_index ? table_index[i] : (int32_t)i) * 256 + tid];
+  load_composite(sh, rank_of + (int64_t)(table_index ? table_index[i] : (int32_t)i) * 256, tid);
   tile_load(tile, raw + i * kRawRecord, 256, tid);
   __syncthreads();
   uint4 wd[8];
