@@ -150,7 +150,11 @@ __device__ __forceinline__ void raw_record_words(const uint8_t* rec, int tid, Em
 // exclusive rank and merged, low and high bytes interleaved.
 // The scheme is the one the format was laid out for
 // (fragpack/ops/fragpack_common.cuh:92-186).
-template <typename Released, typename Emit>
+// kEagerLow: fetch all low bytes up front (records read straight from global
+// memory, where four serialised fetches inside the word loop would each expose
+// the memory latency) instead of on demand (records staged in shared memory,
+// where the sixteen live registers cost more than the late fetches).
+template <bool kEagerLow = false, typename Released, typename Emit>
 __device__ __forceinline__ void coded_record_words(const uint8_t* rec, int vlen,
                                                    const HeadTables& tab, uint8_t* esc, int tid,
                                                    const PipeConsts& k, Released&& released,
@@ -160,6 +164,11 @@ __device__ __forceinline__ void coded_record_words(const uint8_t* rec, int vlen,
 #pragma unroll
   for (int m = 0; m < 3; ++m)
     sym[m] = reinterpret_cast<const uint2*>(rec + kLowBytes)[m * kOwners + tid];
+  uint4 low[kEagerLow ? 4 : 1];
+  if (kEagerLow) {
+#pragma unroll
+    for (int j = 0; j < 4; ++j) low[j] = reinterpret_cast<const uint4*>(rec)[j * kOwners + tid];
+  }
 
   const uint8_t* var = rec + kDenseBytes;
   const uint16_t* h16 = reinterpret_cast<const uint16_t*>(var);
@@ -264,7 +273,9 @@ __device__ __forceinline__ void coded_record_words(const uint8_t* rec, int vlen,
     // Low bytes are fetched as they are needed (two words per 16-byte chunk):
     // holding all sixteen registers across the loop cost more in lost
     // instruction-level parallelism than the later release of the record costs.
-    if ((st & 1) == 0) lw = reinterpret_cast<const uint4*>(rec)[(st >> 1) * kOwners + tid];
+    if ((st & 1) == 0)
+      lw = kEagerLow ? low[kEagerLow ? st >> 1 : 0]
+                     : reinterpret_cast<const uint4*>(rec)[(st >> 1) * kOwners + tid];
     const uint32_t la = (st & 1) ? lw.z : lw.x;
     const uint32_t lb = (st & 1) ? lw.w : lw.y;
     const uint32_t w[4] = {__byte_perm(la, ha, 0x5140), __byte_perm(la, ha, 0x7362),

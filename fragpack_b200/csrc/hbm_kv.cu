@@ -627,7 +627,7 @@ __device__ __forceinline__ void decode_to_rows(const uint8_t* rec, int vlen, con
   if (vlen > kVarCap)
     raw_record_words(rec, tid, emit);
   else
-    coded_record_words(rec, vlen, tab, esc, tid, k, [] {}, emit);
+    coded_record_words<true>(rec, vlen, tab, esc, tid, k, [] {}, emit);
   __syncthreads();
   tile_store(tile, dst, row_bytes, tid);
 }
