@@ -1,7 +1,7 @@
 """Headline benchmark: decode attention over HBM-resident compressed KV.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
-                    [--workload c2|c3|c5] [--layers R] [--no-graph]
+                    [--workload c2|c3|c4|c5] [--arm fused|plain] [--layers R] [--no-graph]
 
 A "step" is one decode step of the workload: the plan is computed once, then
 every resident layer runs fused decode attention (one query token per
@@ -20,7 +20,14 @@ measured HBM copy bandwidth; ``cpu_baseline`` times the CPU oracle codec plus
 torch CPU fp32 attention on a bounded sample of the same workload.
 
 ``--impl reference`` runs that CPU pipeline alone (all host threads) as the
-reference arm.
+reference arm.  ``--arm plain`` runs the comparison kernel: the same KV stored
+as raw BF16 records and read by the same kernel template without the decode
+step (what a plain BF16 paged read of the same logical KV costs).
+``--impl reference-gpu`` runs the reference's own CUDA kernels (built unmodified
+for sm_100a by oracle/build_ref_kernels.py) over the same records in the same
+harness: the same-GPU kernel comparison.
+``--workload c4`` measures the prefill side (token write, block encode,
+decompression) instead.
 """
 
 from __future__ import annotations
@@ -31,7 +38,6 @@ import os
 from pathlib import Path
 import subprocess
 import sys
-import threading
 import time
 
 import numpy as np
@@ -73,33 +79,35 @@ class ClockSampler:
         "clocks_event_reasons.sw_power_cap"
     )
 
-    def __init__(self, index: int) -> None:
+    def __init__(self, index: int, period_ms: int = 100) -> None:
         self.index = index
+        self.period_ms = period_ms
         self.rows: list[list[str]] = []
-        self._stop = threading.Event()
-        self._thread = threading.Thread(target=self._run, daemon=True)
-
-    def _run(self) -> None:
-        while not self._stop.is_set():
-            try:
-                out = subprocess.run(
-                    ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
-                     "-i", str(self.index)],
-                    capture_output=True, text=True, timeout=5,
-                ).stdout.strip()
-                if out:
-                    self.rows.append([c.strip() for c in out.split(",")])
-            except (OSError, subprocess.SubprocessError):
-                return
-            self._stop.wait(0.1)
+        self._proc: subprocess.Popen | None = None
 
     def __enter__(self) -> "ClockSampler":
-        self._thread.start()
+        # One nvidia-smi process in loop mode: a sample every period without the
+        # start-up cost of a process per sample.
+        try:
+            self._proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                 "-i", str(self.index), "-lms", str(self.period_ms)],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True,
+            )
+        except OSError:
+            self._proc = None
         return self
 
     def __exit__(self, *exc) -> None:
-        self._stop.set()
-        self._thread.join(timeout=10)
+        if self._proc is None:
+            return
+        self._proc.terminate()
+        try:
+            out, _ = self._proc.communicate(timeout=10)
+        except subprocess.TimeoutExpired:
+            self._proc.kill()
+            out, _ = self._proc.communicate()
+        self.rows = [[c.strip() for c in line.split(",")] for line in out.splitlines() if line.strip()]
 
     def summary(self) -> dict:
         sm, mx, reasons = [], [], set()
@@ -237,8 +245,40 @@ def run_ours(args) -> dict:
         decode_attention,
         decode_status,
         decode_units,
+        plain_decode_attention,
         workspace_elems,
     )
+
+    plain = args.arm == "plain"
+    refgpu = args.impl == "reference-gpu"
+    if plain:
+        # Comparison arm: every record raw BF16, read by the kernel without a
+        # decode step.  Same planner, pipeline, softmax, merge and harness.
+        decode_attention = plain_decode_attention
+    if refgpu:
+        # Comparison arm: the reference's own kernels (built unmodified for
+        # sm_100a into oracle/_ref) reading the records this library wrote.
+        from oracle import build_ref_kernels
+
+        ref_mod = build_ref_kernels.module()
+
+        def decode_attention(q, tabs, block_table, seq_lens, scale, units, out, ws, replan):
+            # The reference's host wrapper (fragpack/ops/fused_attn_decode.py:105-171):
+            # its kernel attends 8 query heads per KV head; smaller groups run
+            # zero-padded and are copied back.
+            kvh = tabs.rec_addr.shape[2]
+            group = q.shape[1] // kvh
+            if group == 8:
+                ref_mod.fused_decode(q, tabs.rec_addr, tabs.rec_len, tabs.plut, tabs.slut, block_table,
+                                     seq_lens, ws[0], ws[1], ws[2], out, units, replan, scale)
+                return
+            qp = q.new_zeros(q.shape[0], kvh, 8, 128)
+            qp[:, :, :group] = q.unflatten(1, (kvh, group))
+            op = torch.empty_like(qp)
+            ref_mod.fused_decode(qp.flatten(1, 2), tabs.rec_addr, tabs.rec_len, tabs.plut, tabs.slut,
+                                 block_table, seq_lens, ws[0], ws[1], ws[2], op.flatten(1, 2), units,
+                                 replan, scale)
+            out.unflatten(1, (kvh, group)).copy_(op[:, :, :group])
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -267,16 +307,21 @@ def run_ours(args) -> dict:
     head_slice = slice(rank * per, (rank + 1) * per)
     # Resident layers: all of them when they fit, else as many as the budget holds.
     per_layer = cfg.batch * ((cfg.ctx_max + 127) // 128) * 2 * per * (ap.DENSE_BYTES + 1280)
+    if plain:
+        per_layer += cfg.batch * ((cfg.ctx_max + 127) // 128) * 2 * per * ap.RAW_RECORD_BYTES
     budget = int(args.hbm_budget_gb * 2**30)
     layers = args.layers or max(1, min(cfg.layers, budget // max(per_layer, 1)))
     work = workloads.build_decode_workload(
         cfg, device, seed=args.seed, layers=layers, head_slice=head_slice,
-        keep_layers=(0, layers - 1),
+        keep_layers=(0, layers - 1), plain=plain,
     )
     cfg_built = work.cfg
     B, H, G = cfg_built.batch, cfg_built.kv_heads, cfg_built.group
     sms = torch.cuda.get_device_properties(device).multi_processor_count
     units = decode_units(B, H, sms)
+    if refgpu:
+        # The reference reserves one wave of split capacity (fused_attn_decode.py:58-85).
+        units = B + max(1, (2 * sms) // H) - 1
     sizes = workspace_elems(H, units)
     ws = (
         torch.empty(sizes[0], device=device),
@@ -312,7 +357,7 @@ def run_ours(args) -> dict:
     # Correctness gate before any timing (outputs start as NaN).
     step()
     torch.cuda.synchronize()
-    if decode_status(ws, units):
+    if not refgpu and decode_status(ws, units):
         raise SystemExit("decode kernel reported a timed-out wait")
     worst = mean = 0.0
     for layer in (0, layers - 1):
@@ -349,12 +394,15 @@ def run_ours(args) -> dict:
         run_step()
     barrier()
     start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    with ClockSampler(local) as clocks:
-        start.record()
-        for _ in range(args.steps):
-            run_step()
-        stop.record()
-        barrier()
+    # Sampled from here to the end of the end-to-end loop: the timed region, the
+    # per-launch timing and the end-to-end region all run under it.
+    clocks = ClockSampler(local)
+    clocks.__enter__()
+    start.record()
+    for _ in range(args.steps):
+        run_step()
+    stop.record()
+    barrier()
     ms = start.elapsed_time(stop)
     if dist is not None:
         t = torch.tensor([ms], device=device)
@@ -414,6 +462,7 @@ def run_ours(args) -> dict:
         t = torch.tensor([e2e_ms], device=device)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         e2e_ms = float(t.item())
+    clocks.__exit__()
 
     logical_all = work.logical_bytes * layers * world  # every rank holds an equal head shard
     compressed_layer = float(np.mean(work.compressed_bytes))
@@ -434,6 +483,9 @@ def run_ours(args) -> dict:
         "data": "synthetic (seeded per-channel lognormal-scaled Gaussian BF16 KV, K outlier channels)",
         "config": {
             "workload": cfg.name,
+            "arm": ("the reference's CUDA kernels built for sm_100a, reading this library's records (comparison)"
+                    if refgpu else "plain BF16 records, no decode step (comparison)" if plain
+                    else "fused decode over compressed records"),
             "layers_resident": layers,
             "layers_model": cfg.layers,
             "kv_heads_per_gpu": H,
@@ -455,31 +507,39 @@ def run_ours(args) -> dict:
             "d2h_bytes_per_step": d2h,
             "ms_per_step": e2e_ms,
         },
-        "gpu_launches": args.steps * (1 + 2 * layers),
+        # This library's kernels per step: one planner, then attention + merge per layer.
+        "gpu_launches": 0 if refgpu else args.steps * (1 + 2 * layers),
         "roofline": {
             "bound": "hbm",
-            "kernel": "decode_attn_kernel (duration includes the merge kernel that follows it)",
+            "kernel": ("reference decode_attn" if refgpu else "plain_attn_kernel" if plain
+                       else "decode_attn_kernel") + " (duration includes the merge kernel that follows it)",
             "achieved": achieved,
             "peak": peak,
             "peak_kind": peak_kind,
             "unit": "GB/s",
             "frac": achieved / peak,
-            "traffic": NCU_DRAM_BYTES_PER_LAUNCH.get(name) if not (args.batch or args.ctx) else None,
+            "traffic": (NCU_DRAM_BYTES_PER_LAUNCH.get(name)
+                        if not (args.batch or args.ctx or plain or refgpu) else None),
             "algorithmic_bytes_per_launch": compressed_layer,
             "launch_ms": call_ms,
         },
         "validation": {"max_abs": worst, "mean_abs": mean},
         "clocks": clocks.summary(),
     }
-    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+    if refgpu:
+        line["impl"] = "reference-gpu"
+    if rank == 0 and world == 1 and not args.no_cpu_baseline and not plain and not refgpu:
         sample = sample_for_cpu(work, layers=min(layers, args.cpu_layers), seqs=min(B, args.cpu_seqs))
-        seconds, logical, threads = cpu_pipeline(sample)
+        first, logical, threads = cpu_pipeline(sample)
+        passes = max(1, int(np.ceil(args.cpu_seconds / max(first, 1e-3))))
+        seconds, logical, threads = cpu_pipeline(sample, repeats=passes)
         line["cpu_baseline"] = {
             "value": logical / seconds / 1e12,
             "unit": UNIT,
             "cores": threads,
             "kind": "port",
-            "sample": sample["what"] + f" ({len(sample['lens'])} records, {seconds:.2f} s)",
+            "sample": sample["what"] + f" ({len(sample['lens'])} records; {passes} timed passes of "
+                      f"{seconds:.2f} s each after one warm-up pass)",
         }
     if dist is not None:
         dist.destroy_process_group()
@@ -651,8 +711,12 @@ def main() -> None:
     parser.add_argument("--gpus", type=int, default=1)
     parser.add_argument("--steps", type=int, default=20)
     parser.add_argument("--warmup", type=int, default=5)
-    parser.add_argument("--impl", choices=("ours", "reference"), default="ours")
+    parser.add_argument("--impl", choices=("ours", "reference", "reference-gpu"), default="ours",
+                        help="reference: the CPU codec + attention (the reference arm); reference-gpu: the "
+                             "reference's own CUDA kernels built for sm_100a (extra comparison, 1 GPU)")
     parser.add_argument("--workload", choices=("c2", "c3", "c4", "c5"), default=None)
+    parser.add_argument("--arm", choices=("fused", "plain"), default="fused",
+                        help="plain: the comparison kernel over raw BF16 records of the same KV")
     parser.add_argument("--junk", type=float, default=-1.0, help="c4: junk fraction (default 0.009)")
     parser.add_argument("--overflow", type=int, default=8192, help="c4: overflow records")
     parser.add_argument("--layers", type=int, default=0, help="resident layers (default: what fits)")
@@ -666,7 +730,10 @@ def main() -> None:
     parser.add_argument("--no-cpu-baseline", action="store_true")
     parser.add_argument("--cpu-layers", type=int, default=8)
     parser.add_argument("--cpu-seqs", type=int, default=4)
-    parser.add_argument("--cpu-pairs", type=int, default=8)
+    parser.add_argument("--cpu-pairs", type=int, default=64,
+                        help="reference arm: (sequence, KV head) pairs decoded and attended per step")
+    parser.add_argument("--cpu-seconds", type=float, default=12.0,
+                        help="CPU baseline: seconds of host work to time")
     args = parser.parse_args()
     if args.workload == "c4" and args.impl == "ours":
         line = run_codec(args)

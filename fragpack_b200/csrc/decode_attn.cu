@@ -482,6 +482,276 @@ __global__ void __launch_bounds__(kThreads, 2) decode_attn_kernel(DecodeParams p
   }
 }
 
+// ---------------------------------------------------------------------------
+// Comparison arm: the same split-KV kernel over PLAIN BF16 records (32 KB each,
+// fragment order, the layout of raw / open / overflow records) with no decode
+// step.  Same planner, same ring, same softmax and merge; every record is
+// staged whole through a ring of 32 KB slots.  It answers "what does a plain
+// BF16 paged read of the same logical KV cost on this GPU"; a coded record met
+// here contributes zeros and raises FP_DECODE_NOT_PLAIN in the status word.
+// ---------------------------------------------------------------------------
+struct PlainSmem {
+  __align__(128) uint8_t slots[kSlots][kRawRecord];
+  __align__(16) uint8_t p[2][kPBytes];
+  __align__(16) float ref[2][kConsumerWarps][8];
+  __align__(16) int flag[2][kConsumerWarps];
+  __align__(16) float lsum[kConsumerWarps][8];
+  float mrow[8];
+  __align__(16) uint2 qfrag[8][32];
+  int raw[kSlots];
+  __align__(8) uint64_t full[kSlots];
+  __align__(8) uint64_t empty[kSlots];
+  int abort;
+};
+static_assert(sizeof(PlainSmem) <= (228 * 1024) / 2 - 1024, "PlainSmem too large for two CTAs per SM");
+
+__device__ __forceinline__ void plain_produce(const DecodeParams& p, PlainSmem& sm) {
+  const int lane = threadIdx.x & 31;
+  volatile int* abort = &sm.abort;
+  const int n_items = p.plan[1] * p.kvh;
+  uint32_t r = 0;
+  for (int item = blockIdx.x; item < n_items; item += gridDim.x) {
+    Item it;
+    if (!load_item(p, item, it)) continue;
+    const int32_t* bt = p.block_table + (int64_t)it.seq_index * p.bt_stride + it.first_page;
+    for (int base = 0; base < it.pages; base += 32) {
+      const int page = base + lane;
+      int64_t addr_k = 0, addr_v = 0;
+      int32_t len_k = 0, len_v = 0;
+      if (page < it.pages) {
+        const int64_t idx = ((int64_t)bt[page] * 2) * p.kvh + it.head;
+        addr_k = p.rec_addr[idx];
+        addr_v = p.rec_addr[idx + p.kvh];
+        len_k = p.rec_len[idx];
+        len_v = p.rec_len[idx + p.kvh];
+      }
+      const int count = min(32, it.pages - base);
+      for (int j = 0; j < 2 * count; ++j) {
+        const int src = j >> 1;
+        const int64_t addr = __shfl_sync(0xffffffffu, (j & 1) ? addr_v : addr_k, src);
+        const int32_t vlen = __shfl_sync(0xffffffffu, (j & 1) ? len_v : len_k, src);
+        const uint32_t slot = r % kSlots, use = r / kSlots;
+        if (lane == 0) {
+          bool ok = true;
+          if (use > 0) ok = bounded_wait(&sm.empty[slot], (use - 1) & 1, abort, p.status);
+          if (ok) {
+            const bool raw = vlen > kVarCap;
+            sm.raw[slot] = raw;
+            if (raw) {
+              mbar_expect_tx(&sm.full[slot], kRawRecord);
+              bulk_load(sm.slots[slot], reinterpret_cast<const void*>(addr), kRawRecord,
+                        &sm.full[slot]);
+            } else {
+              atomicOr(p.status, FP_DECODE_NOT_PLAIN);
+              mbar_arrive(&sm.full[slot]);
+            }
+          }
+        }
+        ++r;
+        __syncwarp();
+        if (*abort) return;
+      }
+    }
+  }
+}
+
+__device__ __forceinline__ void plain_consume(const DecodeParams& p, PlainSmem& sm) {
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int g = lane >> 2, c = lane & 3;
+  volatile int* abort = &sm.abort;
+  const int n_items = p.plan[1] * p.kvh;
+  uint32_t r = 0, pages = 0;
+
+  // Owner words of the record in `slot` (zeros for a record that is not plain),
+  // in two halves of four 16-byte words to stay inside the register budget;
+  // the slot goes back to the producer once the warp has read its last word.
+  auto record_words = [&](uint32_t slot, auto&& emit) {
+    const uint4* src = reinterpret_cast<const uint4*>(sm.slots[slot]);
+    const bool raw = sm.raw[slot] != 0;
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+      uint4 v[4];
+#pragma unroll
+      for (int x = 0; x < 4; ++x)
+        v[x] = raw ? src[(4 * half + x) * kOwners + tid] : make_uint4(0u, 0u, 0u, 0u);
+      if (half == 1) {
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&sm.empty[slot]);
+      }
+#pragma unroll
+      for (int x = 0; x < 4; ++x) {
+        const uint32_t w[4] = {v[x].x, v[x].y, v[x].z, v[x].w};
+        emit(4 * half + x, w);
+      }
+    }
+  };
+
+  for (int item = blockIdx.x; item < n_items; item += gridDim.x) {
+    Item it;
+    if (!load_item(p, item, it)) continue;
+    {
+      const uint32_t* q =
+          p.q + (int64_t)it.seq_index * p.q_stride + (int64_t)(it.head * p.group + g) * 64;
+      const int st = warp;
+      sm.qfrag[st][lane] = g < p.group ? make_uint2(q[8 * st + c], q[8 * st + 4 + c])
+                                        : make_uint2(0u, 0u);
+    }
+    consumer_barrier();
+    float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+    float o[4] = {0.f, 0.f, 0.f, 0.f};
+
+    for (int i = 0; i < it.pages; ++i, ++pages) {
+      const int buf = pages & 1;
+      const int page_tok0 = (it.first_page + i) * 128;
+      float s[4] = {0.f, 0.f, 0.f, 0.f};
+      {
+        const uint32_t slot = r % kSlots;
+        bounded_wait(&sm.full[slot], (r / kSlots) & 1, abort, p.status);
+        record_words(slot, [&](int st, const uint32_t (&w)[4]) {
+          const uint2 qb = sm.qfrag[st][lane];
+          mma_16816(s, w[0], w[2], w[1], w[3], qb.x, qb.y);
+        });
+        ++r;
+      }
+      const int tok = page_tok0 + 16 * warp + g;
+      const bool in0 = tok < it.seq_len, in1 = tok + 8 < it.seq_len;
+      s[0] = in0 ? s[0] * p.scale_log2 : -INFINITY;
+      s[1] = in0 ? s[1] * p.scale_log2 : -INFINITY;
+      s[2] = in1 ? s[2] * p.scale_log2 : -INFINITY;
+      s[3] = in1 ? s[3] * p.scale_log2 : -INFINITY;
+      float mx[2] = {fmaxf(s[0], s[2]), fmaxf(s[1], s[3])};
+#pragma unroll
+      for (int x = 4; x < 32; x <<= 1) {
+        mx[0] = fmaxf(mx[0], __shfl_xor_sync(0xffffffffu, mx[0], x));
+        mx[1] = fmaxf(mx[1], __shfl_xor_sync(0xffffffffu, mx[1], x));
+      }
+      const bool raised = __any_sync(0xffffffffu, mx[0] > m_run[0] || mx[1] > m_run[1]);
+      if (g == 0) *reinterpret_cast<float2*>(&sm.ref[buf][warp][2 * c]) = make_float2(mx[0], mx[1]);
+      if (lane == 0) sm.flag[buf][warp] = raised;
+      uint8_t* prow = sm.p[buf];
+      auto put_p = [&](const float (&pv)[4]) {
+#pragma unroll
+        for (int jj = 0; jj < 2; ++jj)
+#pragma unroll
+          for (int e = 0; e < 2; ++e) {
+            const int head = 2 * c + e;
+            *reinterpret_cast<__nv_bfloat16*>(prow + (head * 4 + (g >> 1)) * kPRow +
+                                              4 * (2 * warp + jj) + 2 * (g & 1)) =
+                __float2bfloat16_rn(pv[2 * jj + e]);
+          }
+      };
+      float pv[4];
+      if (!raised) {
+#pragma unroll
+        for (int x = 0; x < 4; ++x) pv[x] = fast_exp2(s[x] - m_run[x & 1]);
+        put_p(pv);
+      }
+      consumer_barrier();
+      {
+        const int4 f0 = *reinterpret_cast<const int4*>(&sm.flag[buf][0]);
+        const int4 f1 = *reinterpret_cast<const int4*>(&sm.flag[buf][4]);
+        if (f0.x | f0.y | f0.z | f0.w | f1.x | f1.y | f1.z | f1.w) {
+          float m_new[2] = {m_run[0], m_run[1]};
+#pragma unroll
+          for (int w = 0; w < kConsumerWarps; ++w) {
+            const float2 t = *reinterpret_cast<const float2*>(&sm.ref[buf][w][2 * c]);
+            m_new[0] = fmaxf(m_new[0], t.x);
+            m_new[1] = fmaxf(m_new[1], t.y);
+          }
+#pragma unroll
+          for (int e = 0; e < 2; ++e) {
+            const float base = m_new[e] == -INFINITY ? 0.f : m_new[e];
+            const float alpha = fast_exp2(m_run[e] - base);
+            l_run[e] *= alpha;
+            o[e] *= alpha;
+            o[2 + e] *= alpha;
+            pv[e] = fast_exp2(s[e] - base);
+            pv[2 + e] = fast_exp2(s[2 + e] - base);
+            m_run[e] = m_new[e];
+          }
+          put_p(pv);
+          consumer_barrier();
+        }
+      }
+      l_run[0] += pv[0] + pv[2];
+      l_run[1] += pv[1] + pv[3];
+      {
+        const uint32_t slot = r % kSlots;
+        bounded_wait(&sm.full[slot], (r / kSlots) & 1, abort, p.status);
+        const uint4* pw = reinterpret_cast<const uint4*>(prow + (g * 4 + c) * kPRow);
+        const int rem = it.seq_len - page_tok0;
+        uint4 b;
+        record_words(slot, [&](int st, const uint32_t (&w)[4]) {
+          uint32_t a[4] = {w[0], w[1], w[2], w[3]};
+          if (rem < 128) {
+            // Stale bytes beyond the last token of an open block must not meet
+            // a zero probability as NaN / Inf.
+#pragma unroll
+            for (int x = 0; x < 4; ++x) {
+              const int t0 = 16 * st + 8 * (x & 1) + 2 * c;
+              if (t0 >= rem) a[x] = 0u;
+              else if (t0 + 1 >= rem) a[x] &= 0xffffu;
+            }
+          }
+          if ((st & 1) == 0) b = pw[st >> 1];
+          mma_16816(o, a[0], a[2], a[1], a[3], (st & 1) ? b.z : b.x, (st & 1) ? b.w : b.y);
+        });
+        ++r;
+      }
+    }
+
+    const int64_t row0 = ((int64_t)it.head * p.units + it.unit) * 8;
+#pragma unroll
+    for (int jj = 0; jj < 2; ++jj)
+#pragma unroll
+      for (int e = 0; e < 2; ++e)
+        p.opart[(row0 + 2 * c + e) * 128 + 16 * warp + 8 * jj + g] = o[2 * jj + e];
+    float l[2] = {l_run[0], l_run[1]};
+#pragma unroll
+    for (int x = 4; x < 32; x <<= 1) {
+      l[0] += __shfl_xor_sync(0xffffffffu, l[0], x);
+      l[1] += __shfl_xor_sync(0xffffffffu, l[1], x);
+    }
+    if (g == 0) *reinterpret_cast<float2*>(&sm.lsum[warp][2 * c]) = make_float2(l[0], l[1]);
+    if (warp == 0 && g == 0)
+      *reinterpret_cast<float2*>(&sm.mrow[2 * c]) = make_float2(m_run[0], m_run[1]);
+    consumer_barrier();
+    if (tid < 8) {
+      float sum = 0.f;
+#pragma unroll
+      for (int w = 0; w < kConsumerWarps; ++w) sum += sm.lsum[w][tid];
+      p.ml[(row0 + tid) * 2] = sm.mrow[tid];
+      p.ml[(row0 + tid) * 2 + 1] = sum;
+    }
+  }
+}
+
+__global__ void __launch_bounds__(kThreads, 2) plain_attn_kernel(DecodeParams p) {
+  extern __shared__ __align__(128) uint8_t dyn[];
+  PlainSmem& sm = *reinterpret_cast<PlainSmem*>(dyn);
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kSlots; ++s) {
+      mbar_init(&sm.full[s], 1);
+      mbar_init(&sm.empty[s], kConsumerWarps);
+    }
+    sm.abort = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncthreads();
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  if (threadIdx.x >= kConsumers) {
+    plain_produce(p, sm);
+  } else {
+    plain_consume(p, sm);
+  }
+  __syncthreads();
+  if (sm.abort && threadIdx.x == 0) {
+    const long long t0 = clock64();
+    while (clock64() - t0 < 20000000LL) {
+    }
+  }
+}
+
 // Merges the chunk partials of every sequence into BF16 out[B, H * group, 128]:
 // grid (B, H), one warp per query head, four dims per lane.  Rows without
 // context (CUDA-graph padding) become zeros.  A separate launch on purpose:
@@ -663,36 +933,28 @@ int device_sms() {
 
 using namespace fpb;
 
-extern "C" {
+namespace {
 
-int fp_decode_workspace(int32_t kv_heads, int32_t units, int64_t* opart_elems, int64_t* ml_elems,
-                        int64_t* plan_elems) {
-  FP_REQUIRE(kv_heads > 0 && units > 0, "bad workspace geometry");
-  const int64_t rows = (int64_t)kv_heads * units * 8;
-  if (opart_elems) *opart_elems = rows * 128;
-  if (ml_elems) *ml_elems = rows * 2;
-  if (plan_elems) *plan_elems = plan_words(units);
-  return FP_OK;
-}
-
-int fp_fused_decode(const void* q, int64_t q_stride, const int64_t* rec_addr,
-                    const int32_t* rec_len, const int32_t* plut, const uint8_t* slut,
-                    const int32_t* block_table, int64_t bt_stride, const int32_t* seq_lens,
-                    float* opart, int64_t opart_elems, float* ml, int64_t ml_elems, int32_t* plan,
-                    int64_t plan_elems, void* out, int64_t out_stride, int32_t batch,
-                    int32_t kv_heads, int32_t group, int32_t units, int32_t replan, float scale,
-                    int32_t num_sms, void* stream) {
+// Shared body of fp_fused_decode and fp_plain_decode: argument checks, planner,
+// attention kernel (`plain` selects the comparison arm), merge kernel.
+int launch_decode(bool plain, const void* q, int64_t q_stride, const int64_t* rec_addr,
+                  const int32_t* rec_len, const int32_t* plut, const uint8_t* slut,
+                  const int32_t* block_table, int64_t bt_stride, const int32_t* seq_lens,
+                  float* opart, int64_t opart_elems, float* ml, int64_t ml_elems, int32_t* plan,
+                  int64_t plan_elems, void* out, int64_t out_stride, int32_t batch,
+                  int32_t kv_heads, int32_t group, int32_t units, int32_t replan, float scale,
+                  int32_t num_sms, void* stream) {
   if (batch == 0) return FP_OK;
   FP_REQUIRE(batch > 0 && kv_heads > 0, "bad batch %d / kv_heads %d", batch, kv_heads);
   FP_REQUIRE(group == 1 || group == 2 || group == 4 || group == 8,
              "query group %d must be 1, 2, 4 or 8", group);
   FP_REQUIRE(units >= batch, "decode needs at least one unit per sequence");
-  FP_REQUIRE(q && rec_addr && rec_len && plut && slut && block_table && seq_lens && opart && ml &&
-                 plan && out,
+  FP_REQUIRE(q && rec_addr && rec_len && (plain || (plut && slut)) && block_table && seq_lens &&
+                 opart && ml && plan && out,
              "null decode argument");
   FP_REQUIRE(q_stride % 2 == 0 && reinterpret_cast<uintptr_t>(q) % 4 == 0,
              "q rows must be 4-byte aligned");
-  FP_REQUIRE(reinterpret_cast<uintptr_t>(slut) % 16 == 0, "slut must be 16-byte aligned");
+  FP_REQUIRE(plain || reinterpret_cast<uintptr_t>(slut) % 16 == 0, "slut must be 16-byte aligned");
   FP_REQUIRE(opart_elems >= (int64_t)kv_heads * units * 8 * 128 &&
                  ml_elems >= (int64_t)kv_heads * units * 16,
              "decode workspace too small");
@@ -730,10 +992,11 @@ int fp_fused_decode(const void* q, int64_t q_stride, const int64_t* rec_addr,
   p.units = units;
   p.scale_log2 = scale * 1.4426950408889634f;
   p.k = pipe_consts();
-  const int smem = (int)sizeof(Smem);
-  if (int rc = cuda_status(cudaFuncSetAttribute(decode_attn_kernel,
-                                                cudaFuncAttributeMaxDynamicSharedMemorySize, smem),
-                           "cudaFuncSetAttribute(decode_attn_kernel)"))
+  void (*kernel)(DecodeParams) = plain ? plain_attn_kernel : decode_attn_kernel;
+  const char* name = plain ? "plain_attn_kernel" : "decode_attn_kernel";
+  const int smem = plain ? (int)sizeof(PlainSmem) : (int)sizeof(Smem);
+  if (int rc = cuda_status(
+          cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem), name))
     return rc;
   const long long max_items = (long long)units * kv_heads;
   const int grid = (int)(max_items < slots ? max_items : slots);
@@ -748,8 +1011,7 @@ int fp_fused_decode(const void* q, int64_t q_stride, const int64_t* rec_addr,
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    if (int rc = cuda_status(cudaLaunchKernelEx(&cfg, decode_attn_kernel, p), "decode_attn_kernel"))
-      return rc;
+    if (int rc = cuda_status(cudaLaunchKernelEx(&cfg, kernel, p), name)) return rc;
   }
   {
     // Programmatic dependent launch: the merge may be scheduled while the
@@ -775,6 +1037,44 @@ int fp_fused_decode(const void* q, int64_t q_stride, const int64_t* rec_addr,
   }
   FP_LAUNCH_CHECK("combine_kernel");
   return FP_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int fp_decode_workspace(int32_t kv_heads, int32_t units, int64_t* opart_elems, int64_t* ml_elems,
+                        int64_t* plan_elems) {
+  FP_REQUIRE(kv_heads > 0 && units > 0, "bad workspace geometry");
+  const int64_t rows = (int64_t)kv_heads * units * 8;
+  if (opart_elems) *opart_elems = rows * 128;
+  if (ml_elems) *ml_elems = rows * 2;
+  if (plan_elems) *plan_elems = plan_words(units);
+  return FP_OK;
+}
+
+int fp_fused_decode(const void* q, int64_t q_stride, const int64_t* rec_addr,
+                    const int32_t* rec_len, const int32_t* plut, const uint8_t* slut,
+                    const int32_t* block_table, int64_t bt_stride, const int32_t* seq_lens,
+                    float* opart, int64_t opart_elems, float* ml, int64_t ml_elems, int32_t* plan,
+                    int64_t plan_elems, void* out, int64_t out_stride, int32_t batch,
+                    int32_t kv_heads, int32_t group, int32_t units, int32_t replan, float scale,
+                    int32_t num_sms, void* stream) {
+  return launch_decode(false, q, q_stride, rec_addr, rec_len, plut, slut, block_table, bt_stride,
+                       seq_lens, opart, opart_elems, ml, ml_elems, plan, plan_elems, out,
+                       out_stride, batch, kv_heads, group, units, replan, scale, num_sms, stream);
+}
+
+int fp_plain_decode(const void* q, int64_t q_stride, const int64_t* rec_addr,
+                    const int32_t* rec_len, const int32_t* block_table, int64_t bt_stride,
+                    const int32_t* seq_lens, float* opart, int64_t opart_elems, float* ml,
+                    int64_t ml_elems, int32_t* plan, int64_t plan_elems, void* out,
+                    int64_t out_stride, int32_t batch, int32_t kv_heads, int32_t group,
+                    int32_t units, int32_t replan, float scale, int32_t num_sms, void* stream) {
+  return launch_decode(true, q, q_stride, rec_addr, rec_len, nullptr, nullptr, block_table,
+                       bt_stride, seq_lens, opart, opart_elems, ml, ml_elems, plan, plan_elems,
+                       out, out_stride, batch, kv_heads, group, units, replan, scale, num_sms,
+                       stream);
 }
 
 /*

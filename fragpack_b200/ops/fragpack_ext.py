@@ -59,6 +59,9 @@ _SIGNATURES = {
     "fp_fused_decode": [c_ptr, c_i64, c_ptr, c_ptr, c_ptr, c_ptr, c_ptr, c_i64, c_ptr, c_ptr, c_i64,
                         c_ptr, c_i64, c_ptr, c_i64, c_ptr, c_i64, c_i32, c_i32, c_i32, c_i32, c_i32,
                         c_f32, c_i32, c_ptr],
+    "fp_plain_decode": [c_ptr, c_i64, c_ptr, c_ptr, c_ptr, c_i64, c_ptr, c_ptr, c_i64, c_ptr, c_i64,
+                        c_ptr, c_i64, c_ptr, c_i64, c_i32, c_i32, c_i32, c_i32, c_i32, c_f32, c_i32,
+                        c_ptr],
     "fp_fused_decode_noalloc": [c_ptr, c_i64, c_ptr, c_ptr, c_ptr, c_ptr, c_ptr, c_i64, c_ptr, c_ptr,
                                 c_i64, c_i32, c_i32, c_i32, c_i32, c_i32, c_f32, c_i32, c_ptr],
     "fp_hbm_prepare": [c_ptr, c_ptr, c_i64, c_ptr, c_i64, c_i32, c_ptr],

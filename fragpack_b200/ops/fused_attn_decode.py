@@ -38,6 +38,7 @@ GQA = 8
 SPLIT_WAVES = 8
 # Bits of the status word (include/fragpack_b200.h).
 DECODE_WAIT_TIMEOUT = 1
+DECODE_NOT_PLAIN = 2
 
 
 @dataclass(frozen=True)
@@ -99,6 +100,29 @@ def _sm_count(index: int) -> int:
     return torch.cuda.get_device_properties(index).multi_processor_count
 
 
+def _check_decode_args(q, tables, block_table, seq_lens, out, workspace):
+    """Shape / dtype checks shared by the decode entry points; returns (kv_heads, group, workspace)."""
+    kv_heads = tables.rec_addr.shape[2]
+    group = q.shape[1] // kv_heads
+    if group == 0 or group * kv_heads != q.shape[1] or GQA % group:
+        raise ValueError(f"query heads {q.shape[1]} need a group dividing {GQA}")
+    require_cuda(q, "q")
+    if q.dim() != 3 or q.shape[2] != 128 or q.stride(2) != 1 or q.stride(1) != 128:
+        raise RuntimeError("q must be [B, H, 128] with contiguous heads")
+    if out.dim() != 3 or out.stride(2) != 1 or out.stride(1) != 128 or out.shape != q.shape:
+        raise RuntimeError("out must be [B, H, 128] with contiguous heads")
+    if q.dtype != torch.bfloat16 or out.dtype != torch.bfloat16:
+        raise RuntimeError("q and out must be bfloat16")
+    if block_table.stride(1) != 1 or block_table.dtype != torch.int32:
+        raise RuntimeError("block_table must be int32 with contiguous rows")
+    if seq_lens.dtype != torch.int32 or not seq_lens.is_contiguous():
+        raise RuntimeError("seq_lens must be contiguous int32")
+    opart, ml, plan = workspace
+    if plan.dtype != torch.int32 or opart.dtype != torch.float32 or ml.dtype != torch.float32:
+        raise RuntimeError("decode workspace must be (float32, float32, int32)")
+    return kv_heads, group, (opart, ml, plan)
+
+
 def decode_attention(
     q: torch.Tensor,
     tables: RecordTables,
@@ -133,30 +157,49 @@ def decode_attention(
     Async/thread-safety:
         Enqueues on the current CUDA stream; not synchronized; allocates nothing.
     """
-    kv_heads = tables.rec_addr.shape[2]
-    group = q.shape[1] // kv_heads
-    if group == 0 or group * kv_heads != q.shape[1] or GQA % group:
-        raise ValueError(f"query heads {q.shape[1]} need a group dividing {GQA}")
-    require_cuda(q, "q")
-    if q.dim() != 3 or q.shape[2] != 128 or q.stride(2) != 1 or q.stride(1) != 128:
-        raise RuntimeError("q must be [B, H, 128] with contiguous heads")
-    if out.dim() != 3 or out.stride(2) != 1 or out.stride(1) != 128 or out.shape != q.shape:
-        raise RuntimeError("out must be [B, H, 128] with contiguous heads")
-    if q.dtype != torch.bfloat16 or out.dtype != torch.bfloat16:
-        raise RuntimeError("q and out must be bfloat16")
-    if block_table.stride(1) != 1 or block_table.dtype != torch.int32:
-        raise RuntimeError("block_table must be int32 with contiguous rows")
-    if seq_lens.dtype != torch.int32 or not seq_lens.is_contiguous():
-        raise RuntimeError("seq_lens must be contiguous int32")
-    opart, ml, plan = workspace
-    if plan.dtype != torch.int32 or opart.dtype != torch.float32 or ml.dtype != torch.float32:
-        raise RuntimeError("decode workspace must be (float32, float32, int32)")
+    kv_heads, group, (opart, ml, plan) = _check_decode_args(q, tables, block_table, seq_lens, out, workspace)
     check(
         extension().fp_fused_decode(
             q.data_ptr(), q.stride(0), tables.rec_addr.data_ptr(), tables.rec_len.data_ptr(),
             tables.plut.data_ptr(), tables.slut.data_ptr(), block_table.data_ptr(),
             block_table.stride(0), seq_lens.data_ptr(), opart.data_ptr(), opart.numel(),
             ml.data_ptr(), ml.numel(), plan.data_ptr(), plan.numel(), out.data_ptr(),
+            out.stride(0), q.shape[0], kv_heads, group, units, int(bool(replan)), float(scale),
+            _sm_count(q.device.index if q.device.index is not None else torch.cuda.current_device()),
+            stream_ptr(),
+        )
+    )
+
+
+def plain_decode_attention(
+    q: torch.Tensor,
+    tables: RecordTables,
+    block_table: torch.Tensor,
+    seq_lens: torch.Tensor,
+    scale: float,
+    units: int,
+    out: torch.Tensor,
+    workspace: tuple[torch.Tensor, torch.Tensor, torch.Tensor],
+    replan: bool,
+) -> None:
+    """Comparison arm: :func:`decode_attention` over plain BF16 records only.
+
+    Every record the batch references must be raw (32,768 bytes in fragment
+    order, ``rec_len > 2048``: open, overflow or never-coded blocks); the decode
+    tables of ``tables`` are not read.  Same planner, pipeline, softmax and
+    merge as the fused kernel without the decode step, so its time is the cost
+    of a plain BF16 paged read of the same logical KV.  A coded record
+    contributes zeros and sets ``DECODE_NOT_PLAIN`` in the status word.  The
+    reference has no counterpart.
+
+    Args, raises and stream behaviour: as :func:`decode_attention`.
+    """
+    kv_heads, group, (opart, ml, plan) = _check_decode_args(q, tables, block_table, seq_lens, out, workspace)
+    check(
+        extension().fp_plain_decode(
+            q.data_ptr(), q.stride(0), tables.rec_addr.data_ptr(), tables.rec_len.data_ptr(),
+            block_table.data_ptr(), block_table.stride(0), seq_lens.data_ptr(), opart.data_ptr(),
+            opart.numel(), ml.data_ptr(), ml.numel(), plan.data_ptr(), plan.numel(), out.data_ptr(),
             out.stride(0), q.shape[0], kv_heads, group, units, int(bool(replan)), float(scale),
             _sm_count(q.device.index if q.device.index is not None else torch.cuda.current_device()),
             stream_ptr(),
@@ -177,8 +220,11 @@ def decode_status(workspace: tuple[torch.Tensor, torch.Tensor, torch.Tensor], un
 __all__ = [
     "GQA",
     "RecordTables",
+    "DECODE_NOT_PLAIN",
+    "DECODE_WAIT_TIMEOUT",
     "decode_attention",
     "decode_status",
     "decode_units",
+    "plain_decode_attention",
     "workspace_elems",
 ]

@@ -145,6 +145,7 @@ def build_decode_workload(
     keep_layers: tuple[int, ...] = (0,),
     keep_seqs: int = 2,
     overflow_records: int = 8192,
+    plain: bool = False,
 ) -> DecodeWorkload:
     """Fill a store with the configuration's KV on ``device``.
 
@@ -159,6 +160,10 @@ def build_decode_workload(
             sequences is kept (as BF16) for validation.
         keep_seqs: Sequences kept per kept layer.
         overflow_records: Capacity of the overflow pool (``FRAGPACK_OVERFLOW``).
+        plain: Build the plain-BF16 comparison workload: tables that match no
+            value of the data, so the encoder sends every closed block to the
+            overflow pool as a raw 32 KiB record; the pool is sized to hold them
+            all (``overflow_records`` is ignored).
 
     Returns:
         The workload.
@@ -182,9 +187,18 @@ def build_decode_workload(
     gen = torch.Generator(device=device)
     gen.manual_seed(seed + 4)
     scales_dev = torch.from_numpy(all_scales).to(device)
-    table = np.stack(
-        [calibrate_on_device(gen, scales_dev[layer], cfg.heavy, cfg.junk) for layer in range(n_layers)]
-    )
+    if plain:
+        # High bytes 0x60..0x75 are magnitudes of 2^65 and more: absent from the
+        # data, so every scalar would be a raw entry and no record codes.
+        table = np.broadcast_to(
+            np.arange(0x60, 0x60 + ap.TABLE_ENTRIES, dtype=np.uint8), (n_layers, 2, heads, ap.TABLE_ENTRIES)
+        ).copy()
+        overflow_records = n_layers * n_blocks * 2 * heads + 64
+    else:
+        table = np.stack(
+            [calibrate_on_device(gen, scales_dev[layer], cfg.heavy, cfg.junk)
+             for layer in range(n_layers)]
+        )
     tables: DeviceTables = device_tables(table, device)
     page = page_bytes(heads)
     arenas = [torch.empty((n_blocks, page), dtype=torch.uint8, device=device) for _ in range(n_layers)]

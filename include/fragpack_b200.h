@@ -50,7 +50,7 @@ enum {
 enum { FP_BLOB_BAD_HEADER = 1, FP_BLOB_BAD_LENGTHS = 2, FP_BLOB_NO_OVERFLOW = 4 };
 
 /* Bits of the decode status word (see fp_fused_decode). */
-enum { FP_DECODE_WAIT_TIMEOUT = 1 };
+enum { FP_DECODE_WAIT_TIMEOUT = 1, FP_DECODE_NOT_PLAIN = 2 };
 
 /*
  * The store state that the reference passes as 13 positional tensors to every
@@ -114,6 +114,23 @@ int fp_fused_decode(const void* q, int64_t q_stride, const int64_t* rec_addr,
                     int64_t plan_elems, void* out, int64_t out_stride, int32_t batch,
                     int32_t kv_heads, int32_t group, int32_t units, int32_t replan, float scale,
                     int32_t num_sms, void* stream);
+
+/*
+ * Comparison arm: the same split-KV decode attention over PLAIN BF16 records
+ * (every record raw, 32,768 bytes in fragment order: rec_len > 2048), with no
+ * decode step.  It measures what a plain BF16 paged read of the same logical
+ * KV costs with the same planner, pipeline, softmax and merge; the reference
+ * has no such kernel (its raw records go through decode_attn,
+ * fragpack/ops/fused_attn_decode.cu:214-404).  Arguments as fp_fused_decode
+ * without the tables.  A coded record met here contributes zeros and sets
+ * FP_DECODE_NOT_PLAIN in the status word.
+ */
+int fp_plain_decode(const void* q, int64_t q_stride, const int64_t* rec_addr,
+                    const int32_t* rec_len, const int32_t* block_table, int64_t bt_stride,
+                    const int32_t* seq_lens, float* opart, int64_t opart_elems, float* ml,
+                    int64_t ml_elems, int32_t* plan, int64_t plan_elems, void* out,
+                    int64_t out_stride, int32_t batch, int32_t kv_heads, int32_t group,
+                    int32_t units, int32_t replan, float scale, int32_t num_sms, void* stream);
 
 /*
  * fp_fused_decode without a caller-provided workspace, for hosts that cannot
