@@ -33,6 +33,8 @@ decompression) instead.
 from __future__ import annotations
 
 import argparse
+import atexit
+import datetime
 import json
 import os
 from pathlib import Path
@@ -71,23 +73,28 @@ def measured_hbm_peak() -> tuple[float, str]:
 
 
 class ClockSampler:
-    """Samples SM clocks and throttle reasons with nvidia-smi while a region runs."""
+    """Samples SM clocks and throttle reasons with nvidia-smi while the GPU is under load.
+
+    One ``nvidia-smi`` process in loop mode runs from :meth:`start` (early: it
+    needs a moment before its first sample) to :meth:`stop`; :meth:`mark_begin`
+    and :meth:`mark_end` bracket the loaded region, and only the samples whose
+    own timestamps fall inside it are summarised.
+    """
 
     FIELDS = (
-        "clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
+        "timestamp,clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
         "clocks_event_reasons.sw_power_cap"
     )
 
-    def __init__(self, index: int, period_ms: int = 100) -> None:
+    def __init__(self, index: int, period_ms: int = 25) -> None:
         self.index = index
         self.period_ms = period_ms
         self.rows: list[list[str]] = []
         self._proc: subprocess.Popen | None = None
+        self._begin = self._end = None
 
-    def __enter__(self) -> "ClockSampler":
-        # One nvidia-smi process in loop mode: a sample every period without the
-        # start-up cost of a process per sample.
+    def start(self) -> "ClockSampler":
         try:
             self._proc = subprocess.Popen(
                 ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
@@ -96,9 +103,16 @@ class ClockSampler:
             )
         except OSError:
             self._proc = None
+        atexit.register(self.stop)  # the child must not outlive a failed run
         return self
 
-    def __exit__(self, *exc) -> None:
+    def mark_begin(self) -> None:
+        self._begin = datetime.datetime.now()
+
+    def mark_end(self) -> None:
+        self._end = datetime.datetime.now()
+
+    def stop(self) -> None:
         if self._proc is None:
             return
         self._proc.terminate()
@@ -107,6 +121,7 @@ class ClockSampler:
         except subprocess.TimeoutExpired:
             self._proc.kill()
             out, _ = self._proc.communicate()
+        self._proc = None
         self.rows = [[c.strip() for c in line.split(",")] for line in out.splitlines() if line.strip()]
 
     def summary(self) -> dict:
@@ -114,11 +129,14 @@ class ClockSampler:
         names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
         for row in self.rows:
             try:
-                sm.append(float(row[0]))
-                mx.append(float(row[1]))
+                when = datetime.datetime.strptime(row[0], "%Y/%m/%d %H:%M:%S.%f")
+                if self._begin and self._end and not (self._begin <= when <= self._end):
+                    continue
+                sm.append(float(row[1]))
+                mx.append(float(row[2]))
             except (ValueError, IndexError):
                 continue
-            for name, cell in zip(names, row[2:6]):
+            for name, cell in zip(names, row[3:7]):
                 if cell.lower().startswith("active"):
                     reasons.add(name)
         return {
@@ -126,6 +144,7 @@ class ClockSampler:
             "sm_max_mhz": max(mx) if mx else None,
             "reasons": sorted(reasons),
             "samples": len(sm),
+            "window": "warm-up, timed steps, per-launch timing and end-to-end steps",
         }
 
 
@@ -292,6 +311,7 @@ def run_ours(args) -> dict:
         dist = dist_mod
         dist.init_process_group("nccl", device_id=device)
 
+    clocks = ClockSampler(local).start()
     name = args.workload or ("c2" if world == 1 else "c5")
     cfg = workloads.CONFIGS[name]
     if args.batch or args.ctx:
@@ -390,14 +410,11 @@ def run_ours(args) -> dict:
             dist.barrier()
         torch.cuda.synchronize()
 
+    clocks.mark_begin()
     for _ in range(max(args.warmup, 3)):
         run_step()
     barrier()
     start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    # Sampled from here to the end of the end-to-end loop: the timed region, the
-    # per-launch timing and the end-to-end region all run under it.
-    clocks = ClockSampler(local)
-    clocks.__enter__()
     start.record()
     for _ in range(args.steps):
         run_step()
@@ -462,7 +479,8 @@ def run_ours(args) -> dict:
         t = torch.tensor([e2e_ms], device=device)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         e2e_ms = float(t.item())
-    clocks.__exit__()
+    clocks.mark_end()
+    clocks.stop()
 
     logical_all = work.logical_bytes * layers * world  # every rank holds an equal head shard
     compressed_layer = float(np.mean(work.compressed_bytes))

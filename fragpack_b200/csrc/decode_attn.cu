@@ -135,6 +135,12 @@ __device__ __forceinline__ void prefetch_l2(const void* src, uint32_t bytes) {
   asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(src), "r"(bytes) : "memory");
 }
 
+// Blocks the calling thread until the grids this launch depends on have
+// completed and their writes are visible (returns at once otherwise).
+__device__ __forceinline__ void grid_dependency_wait() {
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+
 constexpr long long kWaitCycles = 4000000000LL;  // about two seconds
 
 // Waits for `parity` of `bar` to complete, at most kWaitCycles.  Returns false
@@ -208,11 +214,21 @@ __device__ __forceinline__ void produce(const DecodeParams& p, Smem& sm) {
   volatile int* abort = &sm.abort;
   const int n_items = p.plan[1] * p.kvh;
   uint32_t r = 0;  // records issued so far
+  // Under a programmatic dependent launch the preceding grid may still run.
+  // Closed pages and their table entries are never written by a kernel that
+  // can immediately precede this one, so they stream at once; a sequence's last
+  // page (the open block the token writer and the encoder touch) waits.
+  bool synced = false;
   for (int item = blockIdx.x; item < n_items; item += gridDim.x) {
     Item it;
     if (!load_item(p, item, it)) continue;
     const int32_t* bt = p.block_table + (int64_t)it.seq_index * p.bt_stride + it.first_page;
+    const int last_page = ((it.seq_len + 127) >> 7) - 1;
     for (int base = 0; base < it.pages; base += 32) {
+      if (!synced && it.first_page + base + 32 > last_page) {
+        grid_dependency_wait();
+        synced = true;
+      }
       const int page = base + lane;
       int64_t addr_k = 0, addr_v = 0;
       int32_t len_k = 0, len_v = 0;
@@ -265,6 +281,7 @@ __device__ __forceinline__ void consume(const DecodeParams& p, Smem& sm) {
   const int n_items = p.plan[1] * p.kvh;
   uint32_t r = 0;      // records consumed so far (matches the producer's count)
   uint32_t pages = 0;  // pages consumed so far: parity selects the P / ref buffers
+  bool synced = false;
 
   auto release = [&](uint32_t slot) {
     __syncwarp();
@@ -274,6 +291,13 @@ __device__ __forceinline__ void consume(const DecodeParams& p, Smem& sm) {
   for (int item = blockIdx.x; item < n_items; item += gridDim.x) {
     Item it;
     if (!load_item(p, item, it)) continue;
+    if (!synced) {
+      // Queries come from, and partial results may still be read by, the
+      // preceding grids: wait for them here, after the plan lookup, while the
+      // producer already streams records.
+      grid_dependency_wait();
+      synced = true;
+    }
     // Stage this item's Q^T B fragments (head g, zero beyond the group; dims
     // 16 st + 2 c and + 8) and decode tables in shared memory.  The barrier
     // that closed the previous item ordered its last reads before these writes.
@@ -462,10 +486,10 @@ __global__ void __launch_bounds__(kThreads, 2) decode_attn_kernel(DecodeParams p
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   __syncthreads();
-  // Prologue done (barriers initialised).  Under a programmatic dependent
-  // launch the preceding grid may still be running: wait for it before reading
-  // queries or KV, or writing partial results.
-  asm volatile("griddepcontrol.wait;" ::: "memory");
+  // Prologue done (barriers initialised).  Each role waits for the preceding
+  // grid where it first needs it (see produce / consume).  The merge kernel may
+  // become resident now; it waits for this grid to complete before it reads.
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   if (threadIdx.x >= kConsumers) {
     produce(p, sm);
   } else {
@@ -510,11 +534,17 @@ __device__ __forceinline__ void plain_produce(const DecodeParams& p, PlainSmem& 
   volatile int* abort = &sm.abort;
   const int n_items = p.plan[1] * p.kvh;
   uint32_t r = 0;
+  bool synced = false;  // see produce()
   for (int item = blockIdx.x; item < n_items; item += gridDim.x) {
     Item it;
     if (!load_item(p, item, it)) continue;
     const int32_t* bt = p.block_table + (int64_t)it.seq_index * p.bt_stride + it.first_page;
+    const int last_page = ((it.seq_len + 127) >> 7) - 1;
     for (int base = 0; base < it.pages; base += 32) {
+      if (!synced && it.first_page + base + 32 > last_page) {
+        grid_dependency_wait();
+        synced = true;
+      }
       const int page = base + lane;
       int64_t addr_k = 0, addr_v = 0;
       int32_t len_k = 0, len_v = 0;
@@ -561,6 +591,7 @@ __device__ __forceinline__ void plain_consume(const DecodeParams& p, PlainSmem& 
   volatile int* abort = &sm.abort;
   const int n_items = p.plan[1] * p.kvh;
   uint32_t r = 0, pages = 0;
+  bool synced = false;
 
   // Owner words of the record in `slot` (zeros for a record that is not plain),
   // in two halves of four 16-byte words to stay inside the register budget;
@@ -589,6 +620,10 @@ __device__ __forceinline__ void plain_consume(const DecodeParams& p, PlainSmem& 
   for (int item = blockIdx.x; item < n_items; item += gridDim.x) {
     Item it;
     if (!load_item(p, item, it)) continue;
+    if (!synced) {
+      grid_dependency_wait();
+      synced = true;
+    }
     {
       const uint32_t* q =
           p.q + (int64_t)it.seq_index * p.q_stride + (int64_t)(it.head * p.group + g) * 64;
@@ -738,7 +773,7 @@ __global__ void __launch_bounds__(kThreads, 2) plain_attn_kernel(DecodeParams p)
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   __syncthreads();
-  asm volatile("griddepcontrol.wait;" ::: "memory");
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   if (threadIdx.x >= kConsumers) {
     plain_produce(p, sm);
   } else {
@@ -759,6 +794,12 @@ __global__ void __launch_bounds__(kThreads, 2) plain_attn_kernel(DecodeParams p)
 // was measured to cost several microseconds each under load.  The launch is
 // programmatically dependent on the attention kernel, so its blocks are already
 // resident (and past their index arithmetic) when the last partial lands.
+// The kernel is a chain of dependent memory round trips (plan, then partials),
+// so it keeps that chain short: every lane reads the same (max, sum) pairs and
+// needs no shuffle, and sixteen chunks are in flight per round with an online
+// rescale between rounds instead of a separate pass for the maximum.
+constexpr int kMergeRound = 16;
+
 __global__ void __launch_bounds__(256)
 combine_kernel(const float* opart, const float* ml, const int32_t* plan, __nv_bfloat16* out,
                int64_t out_stride, int units, int group) {
@@ -773,32 +814,37 @@ combine_kernel(const float* opart, const float* ml, const int32_t* plan, __nv_bf
   const int2 seq = *reinterpret_cast<const int2*>(plan + 2 + 2 * units + 2 * b);
   const int first = seq.x, chunks = seq.y;
   const int64_t base = ((int64_t)kv_head * units + first) * 8 + head;
-  float top = -INFINITY;
-  for (int s = lane; s < chunks; s += 32) top = fmaxf(top, ml[(base + 8LL * s) * 2]);
-#pragma unroll
-  for (int x = 16; x; x >>= 1) top = fmaxf(top, __shfl_xor_sync(0xffffffffu, top, x));
-  float den = 0.f;
+  float top = -INFINITY, den = 0.f;
   float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-  if (top != -INFINITY) {
-    // Eight chunks per round, all loads issued before the first use.
-    for (int s0 = 0; s0 < chunks; s0 += 8) {
-      float2 mlv[8];
-      float4 part[8];
+  for (int s0 = 0; s0 < chunks; s0 += kMergeRound) {
+    float2 mlv[kMergeRound];
+    float4 part[kMergeRound];
 #pragma unroll
-      for (int k = 0; k < 8; ++k) {
-        const int64_t row = base + 8LL * min(s0 + k, chunks - 1);
-        mlv[k] = *reinterpret_cast<const float2*>(ml + row * 2);
-        part[k] = reinterpret_cast<const float4*>(opart + row * 128)[lane];
-      }
+    for (int k = 0; k < kMergeRound; ++k) {
+      const int64_t row = base + 8LL * min(s0 + k, chunks - 1);
+      mlv[k] = *reinterpret_cast<const float2*>(ml + row * 2);
+      part[k] = reinterpret_cast<const float4*>(opart + row * 128)[lane];
+    }
+    float round_top = top;
 #pragma unroll
-      for (int k = 0; k < 8; ++k) {
-        const float wgt = s0 + k < chunks ? exp2f(mlv[k].x - top) : 0.f;
-        den += wgt * mlv[k].y;
-        acc.x += wgt * part[k].x;
-        acc.y += wgt * part[k].y;
-        acc.z += wgt * part[k].z;
-        acc.w += wgt * part[k].w;
-      }
+    for (int k = 0; k < kMergeRound; ++k)
+      if (s0 + k < chunks) round_top = fmaxf(round_top, mlv[k].x);
+    if (round_top == -INFINITY) continue;  // only chunks without a valid token so far
+    const float keep = exp2f(top - round_top);  // 0 while top is still -inf
+    den *= keep;
+    acc.x *= keep;
+    acc.y *= keep;
+    acc.z *= keep;
+    acc.w *= keep;
+    top = round_top;
+#pragma unroll
+    for (int k = 0; k < kMergeRound; ++k) {
+      const float wgt = s0 + k < chunks ? exp2f(mlv[k].x - top) : 0.f;
+      den += wgt * mlv[k].y;
+      acc.x += wgt * part[k].x;
+      acc.y += wgt * part[k].y;
+      acc.z += wgt * part[k].z;
+      acc.w += wgt * part[k].w;
     }
   }
   const float inv = den > 0.f ? 1.f / den : 0.f;
