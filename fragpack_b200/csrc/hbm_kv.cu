@@ -212,44 +212,148 @@ __global__ void commit_kernel(StoreView v) {
 }
 
 // ---------------------------------------------------------------------------
-// Token writer: hbm_kv.cu:221-255.  grid = tokens, one warp per KV head slice.
-// Scatters a token's K and V rows into the fragment order of its block's
-// staging record (see fp_common.cuh for the owner layout).
+// Token writer (replaces write_kernel, hbm_kv.cu:221-255): scatters tokens'
+// K and V rows into the fragment order of their block's staging record (see
+// fp_common.cuh for the owner layout).
+//
+// Sixteen tokens at offsets 16 i .. 16 i + 15 of one block are a complete
+// piece of the record: for K the 32 owners of row group i (512 contiguous
+// bytes in each of the eight word planes), for V the whole word plane i (4 KB
+// contiguous).  A CTA looks at sixteen consecutive input tokens and handles
+//  * every such group that STARTS at one of them and is complete and
+//    contiguous in the input (the bulk of a prefill): rows are staged in shared
+//    memory and written with 16-byte coalesced stores;
+//  * every token of its sixteen that no complete group covers (sequence ends,
+//    decode steps): 4-byte / 2-byte scattered stores.
+// grid = (ceil(tokens / 16), ceil(H / kWriteHeads)).
 // ---------------------------------------------------------------------------
-__global__ void __launch_bounds__(256)
-write_kernel(StoreView v, const uint16_t* key, const uint16_t* value, int64_t ks0, int64_t ks1,
-             int64_t vs0, int64_t vs1, const int64_t* slots, int layer) {
+constexpr int kWriteHeads = 4;          // KV heads per CTA
+constexpr int kWriteRow = 272;          // bytes per staged token row (256 + pad)
+
+// One token's K and V rows of `head`, scattered (the general path).
+__device__ __forceinline__ void write_token_scatter(const StoreView& v, const uint16_t* key,
+                                                    const uint16_t* value, int64_t ks0,
+                                                    int64_t ks1, int64_t vs0, int64_t vs1,
+                                                    int64_t token, int w, int off, int layer,
+                                                    int head, int pair) {
   const fp_store& s = v.s;
-  const int64_t slot = slots[blockIdx.x];
-  if (slot < 0) return;
-  const int block = (int)(slot >> 7), off = (int)(slot & 127);
-  if (block >= s.NB) return;
-  const int w = s.wslot[block];
-  if (w < 0) return;
   // K: the token is a row of the A fragment; V: it is a column.
   const int k_warp = off >> 4, k_j = (off >> 3) & 1, k_g = off & 7;
   const int v_st = off >> 4, v_f = (off >> 3) & 1, v_c = (off >> 1) & 3, v_e = off & 1;
-  for (int x = threadIdx.x; x < s.H * 64; x += blockDim.x) {
-    const int head = x >> 6, pair = x & 63;  // dims 2 pair, 2 pair + 1
-    {
-      const uint32_t val =
-          *reinterpret_cast<const uint32_t*>(key + blockIdx.x * ks0 + head * ks1 + 2 * pair);
-      const int st = pair >> 3, f = (pair >> 2) & 1, c = pair & 3;
-      const int owner = 32 * k_warp + 4 * k_g + c;
-      uint8_t* rec = v.staging(w, layer, head);
-      *reinterpret_cast<uint32_t*>(rec + 16 * (kOwners * st + owner) + 4 * (2 * k_j + f)) = val;
-    }
-    {
-      const uint32_t val =
-          *reinterpret_cast<const uint32_t*>(value + blockIdx.x * vs0 + head * vs1 + 2 * pair);
-      uint8_t* rec = v.staging(w, layer, s.H + head);
+  {
+    const uint32_t val =
+        *reinterpret_cast<const uint32_t*>(key + token * ks0 + head * ks1 + 2 * pair);
+    const int st = pair >> 3, f = (pair >> 2) & 1, c = pair & 3;
+    const int owner = 32 * k_warp + 4 * k_g + c;
+    uint8_t* rec = v.staging(w, layer, head);
+    *reinterpret_cast<uint32_t*>(rec + 16 * (kOwners * st + owner) + 4 * (2 * k_j + f)) = val;
+  }
+  {
+    const uint32_t val =
+        *reinterpret_cast<const uint32_t*>(value + token * vs0 + head * vs1 + 2 * pair);
+    uint8_t* rec = v.staging(w, layer, s.H + head);
 #pragma unroll
-      for (int q = 0; q < 2; ++q) {
-        const int d = 2 * pair + q;
-        const int owner = 32 * (d >> 4) + 4 * (d & 7) + v_c;
-        *reinterpret_cast<uint16_t*>(rec + 16 * (kOwners * v_st + owner) +
-                                     2 * (4 * ((d >> 3) & 1) + 2 * v_f + v_e)) =
-            (uint16_t)(val >> (16 * q));
+    for (int q = 0; q < 2; ++q) {
+      const int d = 2 * pair + q;
+      const int owner = 32 * (d >> 4) + 4 * (d & 7) + v_c;
+      *reinterpret_cast<uint16_t*>(rec + 16 * (kOwners * v_st + owner) +
+                                   2 * (4 * ((d >> 3) & 1) + 2 * v_f + v_e)) =
+          (uint16_t)(val >> (16 * q));
+    }
+  }
+}
+
+__global__ void __launch_bounds__(256)
+write_kernel(StoreView v, const uint16_t* key, const uint16_t* value, int64_t ks0, int64_t ks1,
+             int64_t vs0, int64_t vs1, const int64_t* slots, int64_t n_tokens, int layer,
+             int vector_ok) {
+  const fp_store& s = v.s;
+  __shared__ __align__(16) uint8_t tile[2][16][kWriteRow];
+  __shared__ int tok_slot[16];   // staging slot of each token, -1: skip the token
+  __shared__ int tok_off[16];    // offset of each token in its block
+  __shared__ int tok_flags[16];  // bit 0: covered by a complete group, bit 1: starts one
+  const int tid = threadIdx.x;
+  const int64_t t0 = (int64_t)blockIdx.x * 16;
+  const int head0 = blockIdx.y * kWriteHeads;
+  const int heads = min(kWriteHeads, s.H - head0);
+
+  if (tid < 16) {
+    const int64_t t = t0 + tid;
+    int w = -1, off = 0, flags = 0;
+    if (t < n_tokens) {
+      const int64_t slot = slots[t];
+      if (slot >= 0 && (slot >> 7) < s.NB) {
+        off = (int)(slot & 127);
+        w = s.wslot[slot >> 7];
+        // The group of this token: offsets (off & ~15) .. + 15 of its block,
+        // complete and contiguous iff the sixteen inputs from `first` map to them.
+        const int64_t first = t - (off & 15), base = slot - (off & 15);
+        if (vector_ok && w >= 0 && first >= 0 && first + 16 <= n_tokens) {
+          bool whole = true;
+          for (int k = 0; k < 16; ++k) whole &= slots[first + k] == base + k;
+          if (whole) flags = 1 | ((off & 15) == 0 ? 2 : 0);
+        }
+      }
+    }
+    tok_slot[tid] = w;
+    tok_off[tid] = off;
+    tok_flags[tid] = flags;
+  }
+  __syncthreads();
+
+  // Tokens outside every complete group.
+  for (int k = 0; k < 16; ++k) {
+    if (tok_slot[k] < 0 || (tok_flags[k] & 1)) continue;
+    for (int x = tid; x < heads * 64; x += 256)
+      write_token_scatter(v, key, value, ks0, ks1, vs0, vs1, t0 + k, tok_slot[k], tok_off[k],
+                          layer, head0 + (x >> 6), x & 63);
+  }
+
+  // Complete groups that start here (their later tokens may belong to the next CTA's sixteen).
+  for (int k = 0; k < 16; ++k) {
+    if (!(tok_flags[k] & 2)) continue;
+    const int w = tok_slot[k], group = tok_off[k] >> 4;
+    const int64_t first = t0 + k;
+    for (int h = 0; h < heads; ++h) {
+      const int head = head0 + h;
+      __syncthreads();  // the previous tile has been read
+      {
+        const int row = tid >> 4, col = tid & 15;  // 16 tokens x 16 chunks of 16 bytes
+        const uint4 kk = *reinterpret_cast<const uint4*>(key + (first + row) * ks0 + head * ks1 + 8 * col);
+        const uint4 vv = *reinterpret_cast<const uint4*>(value + (first + row) * vs0 + head * vs1 + 8 * col);
+        *reinterpret_cast<uint4*>(&tile[0][row][16 * col]) = kk;
+        *reinterpret_cast<uint4*>(&tile[1][row][16 * col]) = vv;
+      }
+      __syncthreads();
+      {
+        // K: thread (st, g, c) owns word st of owner 32 group + 4 g + c: tokens g
+        // and g + 8, dim pairs 16 st + 2 c and + 8.
+        const int st = tid >> 5, g = (tid >> 2) & 7, c = tid & 3;
+        uint4 out;
+        out.x = *reinterpret_cast<const uint32_t*>(&tile[0][g][2 * (16 * st + 2 * c)]);
+        out.y = *reinterpret_cast<const uint32_t*>(&tile[0][g][2 * (16 * st + 8 + 2 * c)]);
+        out.z = *reinterpret_cast<const uint32_t*>(&tile[0][g + 8][2 * (16 * st + 2 * c)]);
+        out.w = *reinterpret_cast<const uint32_t*>(&tile[0][g + 8][2 * (16 * st + 8 + 2 * c)]);
+        uint8_t* rec = v.staging(w, layer, head);
+        *reinterpret_cast<uint4*>(rec + 16 * (kOwners * st + 32 * group + (tid & 31))) = out;
+      }
+      {
+        // V: thread = owner (dw, dg, vc) of word plane `group`: dims 16 dw + dg
+        // and + 8, tokens 2 vc, 2 vc + 1 and + 8.
+        const int dw = tid >> 5, dg = (tid >> 2) & 7, vc = tid & 3;
+        uint32_t out[4];
+#pragma unroll
+        for (int b = 0; b < 2; ++b)
+#pragma unroll
+          for (int f = 0; f < 2; ++f) {
+            const int dim = 16 * dw + 8 * b + dg, tok = 8 * f + 2 * vc;
+            const uint32_t lo = *reinterpret_cast<const uint16_t*>(&tile[1][tok][2 * dim]);
+            const uint32_t hi = *reinterpret_cast<const uint16_t*>(&tile[1][tok + 1][2 * dim]);
+            out[2 * b + f] = lo | (hi << 16);
+          }
+        uint8_t* rec = v.staging(w, layer, s.H + head);
+        *reinterpret_cast<uint4*>(rec + 16 * (kOwners * group + tid)) =
+            make_uint4(out[0], out[1], out[2], out[3]);
       }
     }
   }
@@ -712,9 +816,16 @@ int fp_hbm_write(const fp_store* store, const void* key, int64_t k_stride0, int6
                  (k_stride0 | k_stride1 | v_stride0 | v_stride1) % 2 == 0,
              "key / value rows must be 4-byte aligned");
   StoreView v{*store};
-  write_kernel<<<(unsigned)num_tokens, 256, 0, (cudaStream_t)stream>>>(
+  // 16-byte row loads need aligned bases and strides; otherwise every token
+  // takes the scattered path.
+  const int vector_ok =
+      (reinterpret_cast<uintptr_t>(key) | reinterpret_cast<uintptr_t>(value)) % 16 == 0 &&
+      (k_stride0 | k_stride1 | v_stride0 | v_stride1) % 8 == 0;
+  const dim3 grid((unsigned)((num_tokens + 15) / 16),
+                  (unsigned)((store->H + kWriteHeads - 1) / kWriteHeads));
+  write_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(
       v, static_cast<const uint16_t*>(key), static_cast<const uint16_t*>(value), k_stride0,
-      k_stride1, v_stride0, v_stride1, slot_mapping, layer);
+      k_stride1, v_stride0, v_stride1, slot_mapping, num_tokens, layer, vector_ok);
   FP_LAUNCH_CHECK("write_kernel");
   return FP_OK;
 }
