@@ -355,8 +355,14 @@ def run_ours(args) -> dict:
     ]
     outputs = [torch.full_like(q, float("nan")) for q in queries]
     tabs = [RecordTables(*work.store.layer_tables(layer)) for layer in range(layers)]
-    gather = None
-    if world > 1:
+    gather = peer_gather = None
+    if world > 1 and not plain and not refgpu and args.gather == "peers":
+        from fragpack_b200.ops.tp import PeerGather
+
+        # The merge kernel stores this rank's heads into every rank's o_proj
+        # input over NVLink (peer pointers) and waits for the other ranks.
+        peer_gather = PeerGather(B, H * G, device)
+    elif world > 1:
         from fragpack_b200.ops.tp import HeadGather
 
         gather = HeadGather(B, H * G, torch.bfloat16, device)
@@ -367,11 +373,15 @@ def run_ours(args) -> dict:
                          units, outputs[layer], ws, replan=layer == 0)
 
     def step() -> None:
+        nonlocal oproj_in
         for layer in range(layers):
+            if peer_gather is not None:
+                oproj_in = peer_gather.decode(queries[layer], tabs[layer], work.block_table,
+                                              work.seq_lens, SCALE, units, ws, replan=layer == 0)
+                continue
             attend(layer)
             if gather is not None:
                 # Per-head outputs -> o_proj input layout [B, Hq, 128] on every rank.
-                nonlocal oproj_in
                 oproj_in = gather(outputs[layer])
 
     # Correctness gate before any timing (outputs start as NaN).
@@ -379,6 +389,18 @@ def run_ours(args) -> dict:
     torch.cuda.synchronize()
     if not refgpu and decode_status(ws, units):
         raise SystemExit("decode kernel reported a timed-out wait")
+    if peer_gather is not None:
+        if peer_gather.status():
+            raise SystemExit("a peer did not arrive within the wait limit")
+        # The gathered copy of the last layer holds this rank's heads where the
+        # validation below expects them.
+        lo = rank * H * G
+        last = (layers - 1) & 1
+        outputs[layers - 1].copy_(peer_gather.gathered[last][:, lo : lo + H * G])
+        if layers > 1:
+            # Layer 0's copy has been overwritten by later layers; recompute it locally.
+            attend(0)
+        torch.cuda.synchronize()
     worst = mean = 0.0
     for layer in (0, layers - 1):
         w, m = validate(work, queries, outputs, layer)
@@ -387,7 +409,9 @@ def run_ours(args) -> dict:
     if failed and not args.skip_validation:
         raise SystemExit(f"validation failed: max-abs {worst:.3e}, mean-abs {mean:.3e}")
 
-    use_graph = not args.no_graph and world == 1
+    # NCCL calls stay out of the graph; the peer-store gather is plain kernels
+    # (an even number of calls per replay keeps its two copies alternating).
+    use_graph = not args.no_graph and (world == 1 or (peer_gather is not None and layers % 2 == 0))
     graph = None
     if use_graph:
         side = torch.cuda.Stream()
@@ -464,7 +488,11 @@ def run_ours(args) -> dict:
             queries[layer].copy_(q_host[layer], non_blocking=True)
         run_step()
         for layer in range(layers):
-            out_host[layer].copy_(outputs[layer], non_blocking=True)
+            if peer_gather is not None:
+                lo = rank * H * G
+                out_host[layer].copy_(peer_gather.gathered[layer & 1][:, lo : lo + H * G], non_blocking=True)
+            else:
+                out_host[layer].copy_(outputs[layer], non_blocking=True)
         torch.cuda.current_stream().synchronize()
 
     for _ in range(3):
@@ -510,7 +538,10 @@ def run_ours(args) -> dict:
             "q_heads_per_gpu": H * G,
             "batch": B,
             "context": [int(work.lens_host.min()), int(work.lens_host.max())],
-            "parallelism": f"kv-head shard tp{world}" + (" + NCCL all-gather per layer" if world > 1 else ""),
+            "parallelism": f"kv-head shard tp{world}" + (
+                "" if world == 1 else
+                " + output gather by the merge kernel (peer stores over NVLink)" if peer_gather is not None
+                else " + NCCL all-gather per layer"),
             "cuda_graph": bool(use_graph),
             "l2_policy": "inputs larger than L2: every layer reads distinct pages, "
                          f"{compressed_layer * layers / 2**20:.0f} MiB per step vs 126 MiB L2",
@@ -526,7 +557,7 @@ def run_ours(args) -> dict:
             "ms_per_step": e2e_ms,
         },
         # This library's kernels per step: one planner, then attention + merge per layer.
-        "gpu_launches": 0 if refgpu else args.steps * (1 + 2 * layers),
+        "gpu_launches": 0 if refgpu else args.steps * (1 + (4 if peer_gather is not None else 2) * layers),
         "roofline": {
             "bound": "hbm",
             "kernel": ("reference decode_attn" if refgpu else "plain_attn_kernel" if plain
@@ -737,6 +768,8 @@ def main() -> None:
                         help="plain: the comparison kernel over raw BF16 records of the same KV")
     parser.add_argument("--junk", type=float, default=-1.0, help="c4: junk fraction (default 0.009)")
     parser.add_argument("--overflow", type=int, default=8192, help="c4: overflow records")
+    parser.add_argument("--gather", choices=("peers", "nccl"), default="peers",
+                        help="N > 1: how the per-rank outputs reach every rank's o_proj input")
     parser.add_argument("--layers", type=int, default=0, help="resident layers (default: what fits)")
     parser.add_argument("--hbm-budget-gb", type=float, default=40.0)
     parser.add_argument("--seed", type=int, default=0)

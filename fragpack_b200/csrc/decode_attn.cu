@@ -800,9 +800,23 @@ __global__ void __launch_bounds__(kThreads, 2) plain_attn_kernel(DecodeParams p)
 // rescale between rounds instead of a separate pass for the maximum.
 constexpr int kMergeRound = 16;
 
+// Destinations of the merged rows in a tensor-parallel group (world == 0: the
+// caller's own `out` only) and the flags of the arrival protocol.
+struct PeerOut {
+  __nv_bfloat16* out[FP_MAX_PEERS];
+  int64_t offset;  // elements: copy `buffer` and this rank's first head
+  int world;
+};
+struct PeerFlags {
+  int32_t* flag[FP_MAX_PEERS];
+  int32_t* epoch;
+  int32_t* status;
+  int world, rank;
+};
+
 __global__ void __launch_bounds__(256)
 combine_kernel(const float* opart, const float* ml, const int32_t* plan, __nv_bfloat16* out,
-               int64_t out_stride, int units, int group) {
+               int64_t out_stride, int units, int group, PeerOut dests) {
   const int b = blockIdx.x, kv_head = blockIdx.y;
   const int head = threadIdx.x >> 5, lane = threadIdx.x & 31;
   // Let the next grid in the stream start its prologue now; it waits for this
@@ -848,10 +862,65 @@ combine_kernel(const float* opart, const float* ml, const int32_t* plan, __nv_bf
     }
   }
   const float inv = den > 0.f ? 1.f / den : 0.f;
-  __nv_bfloat162* dst = reinterpret_cast<__nv_bfloat162*>(
-      out + (int64_t)b * out_stride + ((int64_t)kv_head * group + head) * 128 + 4 * lane);
-  dst[0] = __floats2bfloat162_rn(acc.x * inv, acc.y * inv);
-  dst[1] = __floats2bfloat162_rn(acc.z * inv, acc.w * inv);
+  const __nv_bfloat162 lo = __floats2bfloat162_rn(acc.x * inv, acc.y * inv);
+  const __nv_bfloat162 hi = __floats2bfloat162_rn(acc.z * inv, acc.w * inv);
+  const int64_t at = (int64_t)b * out_stride + ((int64_t)kv_head * group + head) * 128 + 4 * lane;
+  if (dests.world == 0) {
+    __nv_bfloat162* dst = reinterpret_cast<__nv_bfloat162*>(out + at);
+    dst[0] = lo;
+    dst[1] = hi;
+  } else {
+    // One 8-byte store per destination rank: 256 contiguous bytes per warp,
+    // through the peer mapping for the other ranks.
+    uint2 v;
+    v.x = *reinterpret_cast<const uint32_t*>(&lo);
+    v.y = *reinterpret_cast<const uint32_t*>(&hi);
+#pragma unroll
+    for (int r = 0; r < FP_MAX_PEERS; ++r)  // constant indices keep the pointers in registers
+      if (r < dests.world) *reinterpret_cast<uint2*>(dests.out[r] + dests.offset + at) = v;
+  }
+}
+
+// Arrival of this rank's merged rows at every rank: runs after the merge kernel
+// (stream order), so the fence below covers every row it stored.  Lane r tells
+// rank r; lane 0 advances the local call counter.
+__global__ void peer_signal_kernel(PeerFlags f) {
+  const int r = threadIdx.x;
+  const int arrived = *f.epoch + 1;
+  __syncwarp();
+  __threadfence_system();
+  int32_t* mine = nullptr;
+#pragma unroll
+  for (int x = 0; x < FP_MAX_PEERS; ++x)
+    if (x == r) mine = f.flag[x];
+  if (r < f.world) {
+    asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(mine + f.rank), "r"(arrived)
+                 : "memory");
+  }
+  if (r == 0) *f.epoch = arrived;
+}
+
+// Waits (bounded) until every rank has arrived `*epoch` times.  Runs after
+// peer_signal_kernel of the same call, so *epoch is this call's number.
+__global__ void peer_wait_kernel(PeerFlags f) {
+  const int r = threadIdx.x;
+  if (r >= f.world) return;
+  const int want = *f.epoch;
+  const int32_t* word = nullptr;
+#pragma unroll
+  for (int x = 0; x < FP_MAX_PEERS; ++x)
+    if (x == f.rank) word = f.flag[x] + r;
+  const long long t0 = clock64();
+  for (;;) {
+    int seen;
+    asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(seen) : "l"(word) : "memory");
+    if (seen - want >= 0) return;
+    if (clock64() - t0 > kWaitCycles) {
+      atomicOr(f.status, FP_PEER_WAIT_TIMEOUT);
+      return;
+    }
+    __nanosleep(200);
+  }
 }
 
 // ---------------------------------------------------------------------------
@@ -983,7 +1052,8 @@ namespace {
 
 // Shared body of fp_fused_decode and fp_plain_decode: argument checks, planner,
 // attention kernel (`plain` selects the comparison arm), merge kernel.
-int launch_decode(bool plain, const void* q, int64_t q_stride, const int64_t* rec_addr,
+int launch_decode(bool plain, const fp_peers* peers, int buffer, const void* q, int64_t q_stride,
+                  const int64_t* rec_addr,
                   const int32_t* rec_len, const int32_t* plut, const uint8_t* slut,
                   const int32_t* block_table, int64_t bt_stride, const int32_t* seq_lens,
                   float* opart, int64_t opart_elems, float* ml, int64_t ml_elems, int32_t* plan,
@@ -996,8 +1066,32 @@ int launch_decode(bool plain, const void* q, int64_t q_stride, const int64_t* re
              "query group %d must be 1, 2, 4 or 8", group);
   FP_REQUIRE(units >= batch, "decode needs at least one unit per sequence");
   FP_REQUIRE(q && rec_addr && rec_len && (plain || (plut && slut)) && block_table && seq_lens &&
-                 opart && ml && plan && out,
+                 opart && ml && plan && (out || peers),
              "null decode argument");
+  PeerOut dests = {};
+  PeerFlags flags = {};
+  if (peers) {
+    FP_REQUIRE(peers->world >= 1 && peers->world <= FP_MAX_PEERS && peers->rank >= 0 &&
+                   peers->rank < peers->world && (buffer == 0 || buffer == 1) && peers->epoch &&
+                   peers->status,
+               "bad peer group (world %d, rank %d, buffer %d)", peers->world, peers->rank, buffer);
+    const int64_t row = (int64_t)peers->world * kv_heads * group * 128;
+    FP_REQUIRE(out_stride >= row, "gathered rows hold %lld elements, stride is %lld",
+               (long long)row, (long long)out_stride);
+    for (int r = 0; r < peers->world; ++r) {
+      FP_REQUIRE(peers->out[r] && peers->flag[r] &&
+                     reinterpret_cast<uintptr_t>(peers->out[r]) % 8 == 0,
+                 "peer %d has no buffer", r);
+      dests.out[r] = static_cast<__nv_bfloat16*>(peers->out[r]);
+      flags.flag[r] = peers->flag[r];
+    }
+    dests.offset = (int64_t)buffer * batch * out_stride + (int64_t)peers->rank * kv_heads * group * 128;
+    dests.world = peers->world;
+    flags.epoch = peers->epoch;
+    flags.status = peers->status;
+    flags.world = peers->world;
+    flags.rank = peers->rank;
+  }
   FP_REQUIRE(q_stride % 2 == 0 && reinterpret_cast<uintptr_t>(q) % 4 == 0,
              "q rows must be 4-byte aligned");
   FP_REQUIRE(plain || reinterpret_cast<uintptr_t>(slut) % 16 == 0, "slut must be 16-byte aligned");
@@ -1010,8 +1104,9 @@ int launch_decode(bool plain, const void* q, int64_t q_stride, const int64_t* re
                  reinterpret_cast<uintptr_t>(opart) % 16 == 0 &&
                  reinterpret_cast<uintptr_t>(ml) % 8 == 0,
              "decode workspace must be 16-byte aligned");
-  FP_REQUIRE(out_stride % 2 == 0 && reinterpret_cast<uintptr_t>(out) % 4 == 0,
-             "out rows must be 4-byte aligned");
+  FP_REQUIRE(out_stride % 4 == 0 || (!peers && out_stride % 2 == 0),
+             "out rows must be 4-byte aligned (8-byte in a peer group)");
+  FP_REQUIRE(reinterpret_cast<uintptr_t>(out) % 4 == 0, "out rows must be 4-byte aligned");
   const int sms = num_sms > 0 ? num_sms : device_sms();
   const int slots = 2 * sms;
   cudaStream_t st = (cudaStream_t)stream;
@@ -1077,11 +1172,18 @@ int launch_decode(bool plain, const void* q, int64_t q_stride, const int64_t* re
     const int32_t* plan_c = plan;
     __nv_bfloat16* out_c = static_cast<__nv_bfloat16*>(out);
     if (int rc = cuda_status(cudaLaunchKernelEx(&cfg, combine_kernel, opart_c, ml_c, plan_c, out_c,
-                                                out_stride, (int)units, (int)group),
+                                                out_stride, (int)units, (int)group, dests),
                              "combine_kernel"))
       return rc;
   }
   FP_LAUNCH_CHECK("combine_kernel");
+  if (peers) {
+    // Plain launches: each starts when the kernel before it has completed.
+    peer_signal_kernel<<<1, 32, 0, st>>>(flags);
+    FP_LAUNCH_CHECK("peer_signal_kernel");
+    peer_wait_kernel<<<1, 32, 0, st>>>(flags);
+    FP_LAUNCH_CHECK("peer_wait_kernel");
+  }
   return FP_OK;
 }
 
@@ -1106,9 +1208,24 @@ int fp_fused_decode(const void* q, int64_t q_stride, const int64_t* rec_addr,
                     int64_t plan_elems, void* out, int64_t out_stride, int32_t batch,
                     int32_t kv_heads, int32_t group, int32_t units, int32_t replan, float scale,
                     int32_t num_sms, void* stream) {
-  return launch_decode(false, q, q_stride, rec_addr, rec_len, plut, slut, block_table, bt_stride,
-                       seq_lens, opart, opart_elems, ml, ml_elems, plan, plan_elems, out,
+  return launch_decode(false, nullptr, 0, q, q_stride, rec_addr, rec_len, plut, slut, block_table,
+                       bt_stride, seq_lens, opart, opart_elems, ml, ml_elems, plan, plan_elems, out,
                        out_stride, batch, kv_heads, group, units, replan, scale, num_sms, stream);
+}
+
+int fp_fused_decode_peers(const void* q, int64_t q_stride, const int64_t* rec_addr,
+                          const int32_t* rec_len, const int32_t* plut, const uint8_t* slut,
+                          const int32_t* block_table, int64_t bt_stride, const int32_t* seq_lens,
+                          float* opart, int64_t opart_elems, float* ml, int64_t ml_elems,
+                          int32_t* plan, int64_t plan_elems, const fp_peers* peers,
+                          int32_t buffer, int64_t out_stride, int32_t batch, int32_t kv_heads,
+                          int32_t group, int32_t units, int32_t replan, float scale,
+                          int32_t num_sms, void* stream) {
+  FP_REQUIRE(peers, "null peer group");
+  return launch_decode(false, peers, buffer, q, q_stride, rec_addr, rec_len, plut, slut,
+                       block_table, bt_stride, seq_lens, opart, opart_elems, ml, ml_elems, plan,
+                       plan_elems, nullptr, out_stride, batch, kv_heads, group, units, replan,
+                       scale, num_sms, stream);
 }
 
 int fp_plain_decode(const void* q, int64_t q_stride, const int64_t* rec_addr,
@@ -1117,7 +1234,7 @@ int fp_plain_decode(const void* q, int64_t q_stride, const int64_t* rec_addr,
                     int64_t ml_elems, int32_t* plan, int64_t plan_elems, void* out,
                     int64_t out_stride, int32_t batch, int32_t kv_heads, int32_t group,
                     int32_t units, int32_t replan, float scale, int32_t num_sms, void* stream) {
-  return launch_decode(true, q, q_stride, rec_addr, rec_len, nullptr, nullptr, block_table,
+  return launch_decode(true, nullptr, 0, q, q_stride, rec_addr, rec_len, nullptr, nullptr, block_table,
                        bt_stride, seq_lens, opart, opart_elems, ml, ml_elems, plan, plan_elems,
                        out, out_stride, batch, kv_heads, group, units, replan, scale, num_sms,
                        stream);

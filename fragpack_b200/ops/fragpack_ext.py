@@ -53,12 +53,28 @@ class FpStore(ctypes.Structure):
     ]
 
 
+class FpPeers(ctypes.Structure):
+    """``fp_peers`` of ``include/fragpack_b200.h``."""
+
+    _fields_ = [
+        ("out", c_ptr * 8),
+        ("flag", c_ptr * 8),
+        ("epoch", c_ptr),
+        ("status", c_ptr),
+        ("world", c_i32),
+        ("rank", c_i32),
+    ]
+
+
 # name -> argument types; every function returns int.
 _SIGNATURES = {
     "fp_decode_workspace": [c_i32, c_i32, c_ptr, c_ptr, c_ptr],
     "fp_fused_decode": [c_ptr, c_i64, c_ptr, c_ptr, c_ptr, c_ptr, c_ptr, c_i64, c_ptr, c_ptr, c_i64,
                         c_ptr, c_i64, c_ptr, c_i64, c_ptr, c_i64, c_i32, c_i32, c_i32, c_i32, c_i32,
                         c_f32, c_i32, c_ptr],
+    "fp_fused_decode_peers": [c_ptr, c_i64, c_ptr, c_ptr, c_ptr, c_ptr, c_ptr, c_i64, c_ptr, c_ptr,
+                              c_i64, c_ptr, c_i64, c_ptr, c_i64, c_ptr, c_i32, c_i64, c_i32, c_i32,
+                              c_i32, c_i32, c_i32, c_f32, c_i32, c_ptr],
     "fp_plain_decode": [c_ptr, c_i64, c_ptr, c_ptr, c_ptr, c_i64, c_ptr, c_ptr, c_i64, c_ptr, c_i64,
                         c_ptr, c_i64, c_ptr, c_i64, c_i32, c_i32, c_i32, c_i32, c_i32, c_f32, c_i32,
                         c_ptr],

@@ -52,6 +52,11 @@ enum { FP_BLOB_BAD_HEADER = 1, FP_BLOB_BAD_LENGTHS = 2, FP_BLOB_NO_OVERFLOW = 4 
 /* Bits of the decode status word (see fp_fused_decode). */
 enum { FP_DECODE_WAIT_TIMEOUT = 1, FP_DECODE_NOT_PLAIN = 2 };
 
+/* Bit of fp_peers.status. */
+enum { FP_PEER_WAIT_TIMEOUT = 1 };
+
+#define FP_MAX_PEERS 8
+
 /*
  * The store state that the reference passes as 13 positional tensors to every
  * hbm_* function (fragpack/ops/hbm_kv.py:287-301, hbm_kv.cu:32-78).
@@ -131,6 +136,55 @@ int fp_plain_decode(const void* q, int64_t q_stride, const int64_t* rec_addr,
                     int64_t ml_elems, int32_t* plan, int64_t plan_elems, void* out,
                     int64_t out_stride, int32_t batch, int32_t kv_heads, int32_t group,
                     int32_t units, int32_t replan, float scale, int32_t num_sms, void* stream);
+
+/*
+ * Tensor-parallel decode by KV head with the output exchange done by the merge
+ * kernel itself: every rank writes its heads of every row straight into every
+ * rank's o_proj input buffer through peer pointers (NVLink stores), instead of
+ * writing a local tensor that a collective then gathers.  The reference
+ * declares this head sharding (fragpack/integrations/vllm/backend.py:223-226)
+ * but has no exchange of its own; this replaces the NCCL all-gather a host
+ * would otherwise place after fused_decode.
+ *
+ * One fp_peers per rank.  out[r] / flag[r] are device pointers valid on THIS
+ * rank: the rank's own allocation at index `rank`, peer mappings (symmetric
+ * memory or IPC; plain peer stores and loads only, no multicast) at the others.
+ *   out[r]   rank r's gathered buffer: BF16 [2][B][world * kv_heads * group][128],
+ *            two alternating copies so that a rank ahead by one call cannot
+ *            overwrite rows a slower rank still reads
+ *   flag[r]  rank r's arrival words, int32 [FP_MAX_PEERS]: word s holds the
+ *            number of calls rank s has completed
+ *   epoch    this rank's call counter, int32 [1], zero before the first call
+ *   status   this rank's status word, int32 [1]: FP_PEER_WAIT_TIMEOUT is set
+ *            when a peer did not arrive within about two seconds (the rows it
+ *            owes are then invalid; the kernel returns, the context stays usable)
+ */
+typedef struct fp_peers {
+  void* out[FP_MAX_PEERS];
+  int32_t* flag[FP_MAX_PEERS];
+  int32_t* epoch;
+  int32_t* status;
+  int32_t world, rank;
+} fp_peers;
+
+/*
+ * fp_fused_decode for one rank of a KV-head-sharded group.  Arguments as
+ * fp_fused_decode, except that the output goes to copy `buffer` (0 or 1,
+ * alternate it call by call) of every rank's gathered buffer: this rank's
+ * kv_heads * group query heads land at heads [rank * kv_heads * group, ...) of
+ * each row, row stride `out_stride` elements.  The call then signals its
+ * arrival to every rank and enqueues a bounded wait for all ranks' arrivals,
+ * so that work enqueued after it on this stream sees the whole gathered copy.
+ * Every rank must make the same sequence of calls.
+ */
+int fp_fused_decode_peers(const void* q, int64_t q_stride, const int64_t* rec_addr,
+                          const int32_t* rec_len, const int32_t* plut, const uint8_t* slut,
+                          const int32_t* block_table, int64_t bt_stride, const int32_t* seq_lens,
+                          float* opart, int64_t opart_elems, float* ml, int64_t ml_elems,
+                          int32_t* plan, int64_t plan_elems, const fp_peers* peers,
+                          int32_t buffer, int64_t out_stride, int32_t batch, int32_t kv_heads,
+                          int32_t group, int32_t units, int32_t replan, float scale,
+                          int32_t num_sms, void* stream);
 
 /*
  * fp_fused_decode without a caller-provided workspace, for hosts that cannot
