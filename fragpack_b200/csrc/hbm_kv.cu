@@ -7,6 +7,7 @@
 
 #include "fp_api.h"
 #include "fp_common.cuh"
+#include "fp_pipe.cuh"
 
 namespace fpb {
 
@@ -684,16 +685,23 @@ __device__ __forceinline__ void tile_to_words(uint8_t* tile, int kv, int tid, ui
 
 __device__ __forceinline__ void word_to_tile(uint8_t* tile, int kv, const OwnerCoords& o, int st,
                                              const uint32_t (&w)[4]) {
-#pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    const int j = i >> 1, f = i & 1;
-    if (kv == 0) {
-      *reinterpret_cast<uint32_t*>(tile_at(tile, o.row(j), o.col(st, f))) = w[i];
-    } else {
-      const int tok = o.col(st, f), dim = o.row(j);
-      *reinterpret_cast<uint16_t*>(tile_at(tile, tok, dim)) = (uint16_t)w[i];
-      *reinterpret_cast<uint16_t*>(tile_at(tile, tok + 1, dim)) = (uint16_t)(w[i] >> 16);
-    }
+  // The four registers of word st are the four 8 x 8 pieces (j, f) of an
+  // m16n8k16 A fragment, which is also stmatrix's register layout: one
+  // instruction stores all four, K pieces as they are (rows = tokens) and V
+  // pieces transposed (the fragment's rows are dims).  Lane 8 m + r supplies
+  // the address of row r of piece m = 2 j + f: eight scalars, 16 bytes.
+  const int lane = (o.g << 2) | o.c;
+  const int r = lane & 7, j = (lane >> 4) & 1, f = (lane >> 3) & 1;
+  if (kv == 0) {
+    const uint32_t at = smem_addr(tile_at(tile, 16 * o.warp + 8 * j + r, 16 * st + 8 * f));
+    asm volatile("stmatrix.sync.aligned.m8n8.x4.shared.b16 [%0], {%1, %2, %3, %4};" ::"r"(at),
+                 "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3])
+                 : "memory");
+  } else {
+    const uint32_t at = smem_addr(tile_at(tile, 16 * st + 8 * f + r, 16 * o.warp + 8 * j));
+    asm volatile("stmatrix.sync.aligned.m8n8.x4.trans.shared.b16 [%0], {%1, %2, %3, %4};" ::"r"(at),
+                 "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3])
+                 : "memory");
   }
 }
 
@@ -738,18 +746,156 @@ __device__ __forceinline__ void decode_to_rows(const uint8_t* rec, int vlen, con
 
 constexpr int kDecodeSmem = kTileBytes + kEscBytes;
 
-// Prefill decompressor: grid (pages, 2 H).  hbm_kv.cu:452-494.
-__global__ void __launch_bounds__(kOwners)
-gather_kernel(const int32_t* blocks, const int64_t* rec_addr, const int32_t* rec_len,
-              const int32_t* plut, const uint8_t* slut, uint8_t* wk, uint8_t* wv, int H,
-              PipeConsts k) {
+// ---------------------------------------------------------------------------
+// Prefill decompressor (replaces gather_kernel, hbm_kv.cu:452-494): records of
+// the listed blocks -> token-major BF16 pages.
+//
+// Persistent CTAs (two per SM) walk the records r = page * 2 H + rec with a
+// stride of the grid.  A producer warp resolves blocks -> rec_addr / rec_len for
+// 32 records at a time and streams the coded records through a two-slot ring
+// with bulk copies (raw records are read in place after an L2 prefetch), so the
+// table look-ups and the record fetch of the next records overlap the decode of
+// the current one; eight consumer warps decode a record into the swizzled
+// token-major tile and write it out with 16-byte coalesced stores.
+// All waits are bounded; a timeout sets bit 0 of g_gather_status.
+// ---------------------------------------------------------------------------
+constexpr int kGatherSlots = 2;
+constexpr int kGatherThreads = kOwners + 32;
+
+__device__ int32_t g_gather_status;
+
+struct GatherSmem {
+  __align__(16) uint8_t slots[kGatherSlots][kCodedMax];  // bulk copies need 16-byte alignment
+  __align__(16) uint8_t tile[kTileBytes];
+  __align__(16) uint8_t esc[kEscBytes];
+  __align__(16) HeadTables tabs[kGatherSlots];
+  int64_t addr[kGatherSlots];
+  int32_t vlen[kGatherSlots];
+  __align__(8) uint64_t full[kGatherSlots];
+  __align__(8) uint64_t empty[kGatherSlots];
+  int abort;
+};
+static_assert(sizeof(GatherSmem) <= (228 * 1024) / 2 - 1024, "GatherSmem too large for two CTAs per SM");
+
+struct GatherParams {
+  const int32_t* blocks;
+  const int64_t* rec_addr;
+  const int32_t* rec_len;
+  const int32_t* plut;
+  const uint8_t* slut;
+  uint8_t* wk;
+  uint8_t* wv;
+  int64_t records;  // pages * 2 H
+  int H;
+  PipeConsts k;
+};
+
+__device__ __forceinline__ void gather_produce(const GatherParams& p, GatherSmem& sm) {
+  const int lane = threadIdx.x & 31;
+  volatile int* abort = &sm.abort;
+  const int per = 2 * p.H;
+  uint32_t n = 0;  // records issued so far
+  for (int64_t base = blockIdx.x; base < p.records; base += 32LL * gridDim.x) {
+    // Lane L resolves the L-th of the next 32 records of this CTA.
+    const int64_t r = base + (int64_t)lane * gridDim.x;
+    int64_t addr = 0;
+    int32_t vlen = 0, rec = 0;
+    if (r < p.records) {
+      const int64_t page = r / per;
+      rec = (int)(r - page * per);
+      const int64_t idx = (int64_t)p.blocks[page] * per + rec;
+      addr = p.rec_addr[idx];
+      vlen = p.rec_len[idx];
+    }
+    const int64_t left = (p.records - base + gridDim.x - 1) / gridDim.x;
+    const int count = (int)(left < 32 ? left : 32);
+    for (int j = 0; j < count; ++j) {
+      const int64_t a = __shfl_sync(0xffffffffu, addr, j);
+      const int32_t v = __shfl_sync(0xffffffffu, vlen, j);
+      const int32_t t = __shfl_sync(0xffffffffu, rec, j);
+      const uint32_t slot = n % kGatherSlots, use = n / kGatherSlots;
+      if (lane == 0) {
+        bool ok = true;
+        if (use > 0) ok = bounded_wait(&sm.empty[slot], (use - 1) & 1, abort, &g_gather_status);
+        if (ok) {
+          sm.addr[slot] = a;
+          sm.vlen[slot] = v;
+          sm.tabs[slot] = load_tables(p.plut, p.slut, t);
+          if (v > kVarCap || v < kHeaderBytes) {
+            prefetch_l2(reinterpret_cast<const void*>(a), kRawRecord);
+            mbar_arrive(&sm.full[slot]);
+          } else {
+            const uint32_t bytes = (uint32_t)(kDenseBytes + (v & ~15));
+            mbar_expect_tx(&sm.full[slot], bytes);
+            bulk_load(sm.slots[slot], reinterpret_cast<const void*>(a), bytes, &sm.full[slot]);
+          }
+        }
+      }
+      ++n;
+      __syncwarp();
+      if (*abort) return;
+    }
+  }
+}
+
+__device__ __forceinline__ void gather_consume(const GatherParams& p, GatherSmem& sm) {
+  const int tid = threadIdx.x, lane = tid & 31;
+  volatile int* abort = &sm.abort;
+  const int per = 2 * p.H;
+  const OwnerCoords o(tid);
+  uint32_t n = 0;
+  for (int64_t r = blockIdx.x; r < p.records; r += gridDim.x, ++n) {
+    const int64_t page = r / per;
+    const int rec = (int)(r - page * per);
+    const int kv = rec / p.H, head = rec - kv * p.H;
+    const uint32_t slot = n % kGatherSlots;
+    bounded_wait(&sm.full[slot], (n / kGatherSlots) & 1, abort, &g_gather_status);
+    const int32_t vlen = sm.vlen[slot];
+    auto emit = [&](int st, const uint32_t (&w)[4]) { word_to_tile(sm.tile, kv, o, st, w); };
+    auto release = [&] {
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&sm.empty[slot]);
+    };
+    if (vlen > kVarCap || vlen < kHeaderBytes) {
+      const uint8_t* src = reinterpret_cast<const uint8_t*>(sm.addr[slot]);
+      release();
+      raw_record_words(src, tid, emit);
+    } else {
+      const HeadTables tab = sm.tabs[slot];
+      coded_record_words(sm.slots[slot], vlen, tab, sm.esc, tid, p.k, release, emit);
+    }
+    asm volatile("bar.sync 1, %0;" ::"n"(kOwners) : "memory");  // tile complete
+    uint8_t* dst = (kv == 0 ? p.wk : p.wv) + (page * 128 * p.H + head) * 256;
+    tile_store(sm.tile, dst, (int64_t)p.H * 256, tid);
+    asm volatile("bar.sync 1, %0;" ::"n"(kOwners) : "memory");  // tile and escape scratch free
+  }
+}
+
+__global__ void __launch_bounds__(kGatherThreads, 2) gather_kernel(GatherParams p) {
   extern __shared__ __align__(16) uint8_t dyn[];
-  const int rec = blockIdx.y, kv = rec / H, head = rec % H;
-  const int64_t idx = (int64_t)blocks[blockIdx.x] * 2 * H + rec;
-  const HeadTables tab = load_tables(plut, slut, rec);
-  uint8_t* dst = (kv == 0 ? wk : wv) + ((int64_t)blockIdx.x * 128 * H + head) * 256;
-  decode_to_rows(reinterpret_cast<const uint8_t*>(rec_addr[idx]), rec_len[idx], tab, kv, dyn,
-                 dyn + kTileBytes, dst, (int64_t)H * 256, threadIdx.x, k);
+  GatherSmem& sm = *reinterpret_cast<GatherSmem*>(dyn);
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kGatherSlots; ++s) {
+      mbar_init(&sm.full[s], 1);
+      mbar_init(&sm.empty[s], kOwners / 32);
+    }
+    sm.abort = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncthreads();
+  if (threadIdx.x >= kOwners) {
+    gather_produce(p, sm);
+  } else {
+    gather_consume(p, sm);
+  }
+  // Nothing may still be writing this CTA's shared memory when it exits (see
+  // decode_attn_kernel): after a timeout give copies in flight time to land.
+  __syncthreads();
+  if (sm.abort && threadIdx.x == 0) {
+    const long long t0 = clock64();
+    while (clock64() - t0 < 20000000LL) {
+    }
+  }
 }
 
 // Batch decoder: grid = records.
@@ -865,13 +1011,33 @@ int fp_hbm_gather(const int32_t* blocks, int64_t n, const int64_t* rec_addr,
   FP_REQUIRE(workspace_bytes >= n * 128 * (int64_t)kv_heads * 256, "workspace too small");
   FP_REQUIRE((reinterpret_cast<uintptr_t>(wk) | reinterpret_cast<uintptr_t>(wv)) % 16 == 0,
              "workspace must be 16-byte aligned");
-  static int allowed = allow_smem(gather_kernel, kDecodeSmem);
+  static int allowed = allow_smem(gather_kernel, (int)sizeof(GatherSmem));
   if (allowed) return allowed;
-  gather_kernel<<<dim3((unsigned)n, 2 * kv_heads), kOwners, kDecodeSmem, (cudaStream_t)stream>>>(
-      blocks, rec_addr, rec_len, plut, slut, static_cast<uint8_t*>(wk), static_cast<uint8_t*>(wv),
-      kv_heads, pipe_consts());
+  GatherParams p;
+  p.blocks = blocks;
+  p.rec_addr = rec_addr;
+  p.rec_len = rec_len;
+  p.plut = plut;
+  p.slut = slut;
+  p.wk = static_cast<uint8_t*>(wk);
+  p.wv = static_cast<uint8_t*>(wv);
+  p.records = n * 2 * kv_heads;
+  p.H = kv_heads;
+  p.k = pipe_consts();
+  int dev = 0, sms = 148;
+  if (cudaGetDevice(&dev) == cudaSuccess)
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  const int64_t resident = 2LL * sms;
+  const unsigned grid = (unsigned)(p.records < resident ? p.records : resident);
+  gather_kernel<<<grid, kGatherThreads, sizeof(GatherSmem), (cudaStream_t)stream>>>(p);
   FP_LAUNCH_CHECK("gather_kernel");
   return FP_OK;
+}
+
+int fp_hbm_gather_status(int32_t* status) {
+  FP_REQUIRE(status, "null status");
+  return cuda_status(cudaMemcpyFromSymbol(status, g_gather_status, sizeof(int32_t)),
+                     "cudaMemcpyFromSymbol(g_gather_status)");
 }
 
 int fp_encode_records(const void* raw, int64_t n, const uint8_t* rank_of,

@@ -85,6 +85,7 @@ _SIGNATURES = {
     "fp_hbm_encode": [c_ptr, c_ptr, c_i32, c_ptr, c_i64, c_i64, c_ptr],
     "fp_hbm_commit": [c_ptr, c_ptr],
     "fp_hbm_gather": [c_ptr, c_i64, c_ptr, c_ptr, c_ptr, c_ptr, c_ptr, c_ptr, c_i64, c_i32, c_ptr],
+    "fp_hbm_gather_status": [c_ptr],
     "fp_hbm_export": [c_ptr, c_i64, c_ptr, c_ptr, c_ptr, c_i64, c_i64, c_ptr, c_i32, c_i32, c_i32,
                       c_i64, c_ptr],
     "fp_hbm_import": [c_ptr, c_ptr, c_i64, c_ptr, c_ptr, c_i64, c_ptr, c_ptr, c_ptr, c_i64, c_ptr],

@@ -368,6 +368,15 @@ class HbmKvStore:
             )
         )
 
+    @staticmethod
+    def gather_status() -> int:
+        """Status word of the decompressor (synchronises): bit 0 = a bounded wait ran out."""
+        import ctypes
+
+        word = ctypes.c_int32(0)
+        check(extension().fp_hbm_gather_status(ctypes.byref(word)))
+        return int(word.value)
+
     def layer_tables(
         self, layer: int
     ) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor]:

@@ -240,11 +240,18 @@ int fp_hbm_commit(const fp_store* store, void* stream);
 /*
  * hbm_gather (fragpack/ops/hbm_kv.cu:736-753): the prefill decompressor.
  * Decodes records of `blocks[i]` of one layer into token-major BF16 pages
- * wk / wv [>= n, 128, H, 128].
+ * wk / wv [>= n, 128, H, 128].  Its device-side waits are bounded; should one
+ * run out, bit 0 of the status word read by fp_hbm_gather_status is set (the
+ * workspace contents are then invalid).
  */
 int fp_hbm_gather(const int32_t* blocks, int64_t n, const int64_t* rec_addr,
                   const int32_t* rec_len, const int32_t* plut, const uint8_t* slut, void* wk,
                   void* wv, int64_t workspace_bytes, int32_t kv_heads, void* stream);
+
+/* Copies the decompressor's status word to the host (synchronises the device's
+ * prior work on the legacy stream); zero in normal operation.  No counterpart
+ * in the reference. */
+int fp_hbm_gather_status(int32_t* status);
 
 /* hbm_export (fragpack/ops/hbm_kv.cu:755-774): closed blocks -> block blobs. */
 int fp_hbm_export(const int32_t* blocks, int64_t n, const int64_t* rec_addr,
