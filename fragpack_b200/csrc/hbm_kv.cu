@@ -369,6 +369,9 @@ struct EncodeShared {
   // Per high byte: low nibble = 3-bit primary code (7 = escape), high nibble =
   // escape nibble (rank - 7, or 15 for a byte outside the table).
   __align__(16) uint8_t composite[256];
+  // Per 8-bit flag mask: byte selectors (prmt nibbles) listing the flagged
+  // positions in ascending order; unused selectors are 0.
+  uint32_t compact[256];
   int warp_sum[2][8];
   uint8_t* dst;
   int raw;
@@ -380,6 +383,11 @@ __device__ __forceinline__ void load_composite(EncodeShared& sh, const uint8_t* 
   const uint32_t code = min(r, (uint32_t)kPrimaryDirect);
   const uint32_t nib = r < kPrimaryDirect ? 0u : (r < kTableEntries ? r - kPrimaryDirect : 15u);
   sh.composite[tid] = (uint8_t)(code | (nib << 4));
+  uint32_t pick = 0;
+  int k = 0;
+  for (int pos = 0; pos < 8; ++pos)
+    if ((tid >> pos) & 1) pick |= (uint32_t)pos << (4 * k++);
+  sh.compact[tid] = pick;
 }
 
 struct EncodePlan {
@@ -423,22 +431,37 @@ __device__ __forceinline__ void encode_cta(const uint4 (&wd)[8], EncodeShared& s
     const uint32_t hi_b = __byte_perm(wd[st].z, wd[st].w, 0x7531);
     const uint32_t ca = composite4(sh, hi_a), cb = composite4(sh, hi_b);
     codes[st] = low_nibbles(ca) | (low_nibbles(cb) << 16);
-    uint32_t f = (codes[st] + 0x11111111u) & 0x88888888u;  // nibbles equal to 7
-    while (f) {
-      const int pos = (__ffs(f) - 1) >> 2;
-      f &= f - 1;
-      const int shift = 8 * (pos & 3);
-      const uint32_t nib = (((pos < 4) ? ca : cb) >> (shift + 4)) & 15u;
-      if (n_esc < 16) queue |= (uint64_t)nib << (4 * n_esc);
-      if (nib == 15u) {
-        const uint32_t entry = (uint32_t)n_esc | (((((pos < 4) ? hi_a : hi_b) >> shift) & 0xffu) << 16);
+    const uint32_t f = (codes[st] + 0x11111111u) & 0x88888888u;  // nibbles equal to 7
+    // This word's escape nibbles, in order, without a loop over them (lanes
+    // differ in how many they have; a loop runs as long as the worst lane).
+    // Flags -> one byte: the multiply moves flag i of each half to bit 12 + i /
+    // 28 + i; no two partial products meet, so nothing carries.
+    const uint32_t gathered = (f >> 3) * 0x1248u;
+    const uint32_t mask8 = ((gathered >> 12) & 0xfu) | ((gathered >> 24) & 0xf0u);
+    const uint32_t pick = sh.compact[mask8];  // byte selectors that move flagged bytes to the front
+    const uint32_t ea = (ca >> 4) & 0x0f0f0f0fu, eb = (cb >> 4) & 0x0f0f0f0fu;
+    const uint32_t front_lo = __byte_perm(ea, eb, pick), front_hi = __byte_perm(ea, eb, pick >> 16);
+    const int here = __popc(f);
+    uint32_t packed = low_nibbles(front_lo) | (low_nibbles(front_hi) << 16);
+    packed &= here >= 8 ? 0xffffffffu : (1u << (4 * here)) - 1u;  // drop what the padding selected
+    if (n_esc < 16) queue |= (uint64_t)packed << (4 * n_esc);
+    // Raw scalars (nibble 15) are rare.
+    uint32_t raws = packed & (packed >> 1);
+    raws &= (raws >> 2) & 0x11111111u;
+    if (raws) {
+      const uint32_t high_lo = __byte_perm(hi_a, hi_b, pick), high_hi = __byte_perm(hi_a, hi_b, pick >> 16);
+      do {
+        const int k = (__ffs(raws) - 1) >> 2;
+        raws &= raws - 1;
+        const uint32_t high = ((k < 4 ? high_lo : high_hi) >> (8 * (k & 3))) & 0xffu;
+        const uint32_t entry = (uint32_t)(n_esc + k) | (high << 16);
 #pragma unroll
         for (int x = 0; x < 4; ++x)
           if (n_raw == x) raw_q[x] = entry;
         ++n_raw;
-      }
-      ++n_esc;
+      } while (raws);
     }
+    n_esc += here;
   }
   // Symbol words: per 32-scalar group three words; bit 3 of word k's nibble j
   // is bit k of the code of scalar 24 + j (attn_page.py:174-181).
