@@ -59,7 +59,7 @@ FALLBACK_HBM_GBS = 6650.0
 # dram__bytes_read.sum + dram__bytes_write.sum of one decode_attn_kernel launch,
 # from the ncu captures summarised under profiles/ (configuration 2 measured
 # directly; the others are not captured at full size).
-NCU_DRAM_BYTES_PER_LAUNCH = {"c2": 47_636_480 + 100_864}
+NCU_DRAM_BYTES_PER_LAUNCH = {"c2": 47_637_760 + 46_080 + 100_864}
 
 
 def measured_hbm_peak() -> tuple[float, str]:
