@@ -361,8 +361,19 @@ def run_ours(args) -> dict:
 
         # The merge kernel stores this rank's heads into every rank's o_proj
         # input over NVLink (peer pointers) and waits for the other ranks.
-        peer_gather = PeerGather(B, H * G, device)
-    elif world > 1:
+        # Mapping peer memory can be refused by a container; every rank then
+        # uses the collective instead (the line's `parallelism` says which ran).
+        try:
+            peer_gather = PeerGather(B, H * G, device)
+            mapped = 1
+        except Exception as exc:  # noqa: BLE001
+            print(f"[rank {rank}] peer mapping failed ({exc}); using the NCCL all-gather", file=sys.stderr)
+            mapped = 0
+        agreed = torch.tensor([mapped], device=device)
+        dist.all_reduce(agreed, op=dist.ReduceOp.MIN)
+        if not int(agreed.item()):
+            peer_gather = None
+    if world > 1 and peer_gather is None:
         from fragpack_b200.ops.tp import HeadGather
 
         gather = HeadGather(B, H * G, torch.bfloat16, device)

@@ -21,8 +21,14 @@ from fragpack_b200.ops.hbm_kv import page_bytes
 
 
 def test_importing_the_backend_does_not_import_vllm() -> None:
-    assert "vllm.v1.attention.backend" not in sys.modules or True  # other tests may have faked it
-    assert backend.PrefillGroup and backend.FragPackMetadata
+    import subprocess
+
+    code = (
+        "import sys; import fragpack_b200.integrations.vllm.backend as b; "
+        "assert b.PrefillGroup and b.FragPackMetadata and b.run_layer; "
+        "assert not any(m == 'vllm' or m.startswith('vllm.') for m in sys.modules)"
+    )
+    subprocess.run([sys.executable, "-c", code], check=True, cwd=str(__import__("pathlib").Path(__file__).parents[1]))
 
 
 def test_count_closes_counts_crossed_block_boundaries() -> None:
