@@ -377,12 +377,21 @@ struct EncodeShared {
   int raw;
 };
 
+// The composite table is indexed by the high byte rotated left by one bit: the
+// sign moves to bit 0, so +x and -x, and neighbouring exponents, share a 4-byte
+// word.  Real KV uses a handful of exponents with both signs; unrotated, +x and
+// -x sit 128 bytes apart - same bank, different word - and the look-ups of a
+// warp replay on bank conflicts.
+__device__ __forceinline__ uint32_t table_slot(uint32_t high) {
+  return ((high << 1) | (high >> 7)) & 0xffu;
+}
+
 // Fills the composite table from `rank_of` (one entry per thread).
 __device__ __forceinline__ void load_composite(EncodeShared& sh, const uint8_t* rank_of, int tid) {
   const uint32_t r = rank_of[tid];
   const uint32_t code = min(r, (uint32_t)kPrimaryDirect);
   const uint32_t nib = r < kPrimaryDirect ? 0u : (r < kTableEntries ? r - kPrimaryDirect : 15u);
-  sh.composite[tid] = (uint8_t)(code | (nib << 4));
+  sh.composite[table_slot((uint32_t)tid)] = (uint8_t)(code | (nib << 4));
   uint32_t pick = 0;
   int k = 0;
   for (int pos = 0; pos < 8; ++pos)
@@ -397,8 +406,10 @@ struct EncodePlan {
 
 // Composite bytes of the four high bytes packed in `hi`.
 __device__ __forceinline__ uint32_t composite4(const EncodeShared& sh, uint32_t hi) {
-  const uint32_t c0 = sh.composite[hi & 0xffu], c1 = sh.composite[(hi >> 8) & 0xffu];
-  const uint32_t c2 = sh.composite[(hi >> 16) & 0xffu], c3 = sh.composite[hi >> 24];
+  // All four bytes rotated at once (see table_slot).
+  const uint32_t at = ((hi << 1) & 0xfefefefeu) | ((hi >> 7) & 0x01010101u);
+  const uint32_t c0 = sh.composite[at & 0xffu], c1 = sh.composite[(at >> 8) & 0xffu];
+  const uint32_t c2 = sh.composite[(at >> 16) & 0xffu], c3 = sh.composite[at >> 24];
   return c0 | (c1 << 8) | (c2 << 16) | (c3 << 24);
 }
 
@@ -533,7 +544,7 @@ __device__ __forceinline__ void encode_cta(const uint4 (&wd)[8], EncodeShared& s
 #pragma unroll
       for (int e = 0; e < 8; ++e) {
         const uint32_t high = (highs[e >> 2] >> (8 * (e & 3))) & 0xffu;
-        const uint32_t c = sh.composite[high];
+        const uint32_t c = sh.composite[table_slot(high)];
         if ((c & 7u) == (uint32_t)kPrimaryDirect) {
           const uint32_t nib = c >> 4;
           if (n_esc > 16) {
