@@ -50,6 +50,43 @@ def test_argument_errors_need_no_gpu() -> None:
     assert tuple(s.value for s in sizes) == fad.workspace_elems(4, 77)
 
 
+def test_decode_entry_points_reject_bad_geometry_before_any_launch() -> None:
+    """Rejected arguments return FP_ERR_ARGUMENT with a message; nothing is enqueued (no GPU here)."""
+    import ctypes
+
+    from fragpack_b200.ops.fragpack_ext import FpPeers
+
+    lib = extension()
+    fake = 0x1000  # never dereferenced: the checks below fail first
+    common = dict(batch=2, kv_heads=2, units=4)
+
+    def fused(group=8, units=4, plan_elems=10**6, opart_elems=10**9):
+        return lib.fp_fused_decode(fake, 2048, fake, fake, fake, fake, fake, 8, fake, fake, opart_elems,
+                                   fake, 10**9, fake, plan_elems, fake, 2048, common["batch"],
+                                   common["kv_heads"], group, units, 1, 0.088, 148, None)
+
+    assert fused(group=3) == -1 and b"query group" in lib.fp_last_error()
+    assert fused(units=1) == -1 and b"unit" in lib.fp_last_error()
+    assert fused(plan_elems=4) == -1 and b"plan" in lib.fp_last_error()
+    assert fused(opart_elems=16) == -1 and b"workspace" in lib.fp_last_error()
+
+    peers = FpPeers()
+    peers.world, peers.rank = 9, 0
+    peers.epoch = peers.status = fake
+    rc = lib.fp_fused_decode_peers(fake, 2048, fake, fake, fake, fake, fake, 8, fake, fake, 10**9, fake,
+                                   10**9, fake, 10**6, ctypes.byref(peers), 0, 2048 * 9, 2, 2, 8, 4, 1,
+                                   0.088, 148, None)
+    assert rc == -1 and b"peer group" in lib.fp_last_error()
+    peers.world = 2
+    rc = lib.fp_fused_decode_peers(fake, 2048, fake, fake, fake, fake, fake, 8, fake, fake, 10**9, fake,
+                                   10**9, fake, 10**6, ctypes.byref(peers), 2, 4096, 2, 2, 8, 4, 1,
+                                   0.088, 148, None)
+    assert rc == -1 and b"buffer 2" in lib.fp_last_error()
+    rc = lib.fp_fused_decode_noalloc(fake, 2048, fake, fake, fake, fake, fake, 8, fake, fake, 2048, 2, 64,
+                                     8, 5000, 1, 0.088, 148, None)
+    assert rc == -1 and b"built-in decode scratch" in lib.fp_last_error()
+
+
 def test_operators_have_no_cpu_fallback() -> None:
     q = torch.zeros(1, 8, 128, dtype=torch.bfloat16)
     dummy = torch.zeros(1, 2, 1, dtype=torch.int64)
