@@ -349,11 +349,12 @@ def run_ours(args) -> dict:
         torch.empty(sizes[2], dtype=torch.int32, device=device),
     )
     gen = torch.Generator(device=device).manual_seed(args.seed + 100 + rank)
-    queries = [
-        torch.randn(B, H * G, 128, generator=gen, device=device).to(torch.bfloat16)
-        for _ in range(layers)
-    ]
-    outputs = [torch.full_like(q, float("nan")) for q in queries]
+    # One tensor for all layers' queries and one for their outputs, so that the
+    # end-to-end step moves each with a single copy; a layer's call sees its slice.
+    q_all = torch.randn(layers, B, H * G, 128, generator=gen, device=device).to(torch.bfloat16)
+    out_all = torch.full_like(q_all, float("nan"))
+    queries = [q_all[layer] for layer in range(layers)]
+    outputs = [out_all[layer] for layer in range(layers)]
     tabs = [RecordTables(*work.store.layer_tables(layer)) for layer in range(layers)]
     gather = peer_gather = None
     if world > 1 and not plain and not refgpu and args.gather == "peers":
@@ -485,25 +486,26 @@ def run_ours(args) -> dict:
         call_ms = min(call_ms, ms_per_step / layers)
 
     # End to end through the public API with host buffers.
-    q_host = [q.cpu().pin_memory() for q in queries]
-    out_host = [torch.empty_like(q, device="cpu").pin_memory() for q in queries]
+    q_host = q_all.cpu().pin_memory()
+    out_host = torch.empty_like(q_all, device="cpu").pin_memory()
     bt_host = work.block_table.cpu().pin_memory()
     len_host = work.seq_lens.cpu().pin_memory()
-    h2d = sum(q.numel() * 2 for q in q_host) + bt_host.numel() * 4 + len_host.numel() * 4
-    d2h = sum(o.numel() * 2 for o in out_host)
+    h2d = q_host.numel() * 2 + bt_host.numel() * 4 + len_host.numel() * 4
+    d2h = out_host.numel() * 2
 
     def e2e_step() -> None:
         work.block_table.copy_(bt_host, non_blocking=True)
         work.seq_lens.copy_(len_host, non_blocking=True)
-        for layer in range(layers):
-            queries[layer].copy_(q_host[layer], non_blocking=True)
+        q_all.copy_(q_host, non_blocking=True)
         run_step()
-        for layer in range(layers):
-            if peer_gather is not None:
-                lo = rank * H * G
+        if peer_gather is not None:
+            # The result lives in the two gathered copies (the last two layers');
+            # read this rank's heads of each back, the same bytes per layer.
+            lo = rank * H * G
+            for layer in range(layers):
                 out_host[layer].copy_(peer_gather.gathered[layer & 1][:, lo : lo + H * G], non_blocking=True)
-            else:
-                out_host[layer].copy_(outputs[layer], non_blocking=True)
+        else:
+            out_host.copy_(out_all, non_blocking=True)
         torch.cuda.current_stream().synchronize()
 
     for _ in range(3):
