@@ -750,12 +750,15 @@ combine_kernel(const float* opart, const float* ml, const int32_t* plan, __nv_bf
   // Let the next grid in the stream start its prologue now; it waits for this
   // grid before it touches anything this grid reads or writes.
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-  // Everything read below was written by earlier grids: wait for them.
-  asm volatile("griddepcontrol.wait;" ::: "memory");
-  if (head >= group) return;
+  // The plan was complete before the attention grid started, so the sequence's
+  // chunk list is read while that grid may still be running: one dependent
+  // round trip less after it finishes.
   const int2 seq = *reinterpret_cast<const int2*>(plan + 2 + 2 * units + 2 * b);
   const int first = seq.x, chunks = seq.y;
   const int64_t base = ((int64_t)kv_head * units + first) * 8 + head;
+  // The partial results read below are written by the attention grid: wait for it.
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  if (head >= group) return;
   float top = -INFINITY, den = 0.f;
   float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
   for (int s0 = 0; s0 < chunks; s0 += kMergeRound) {
