@@ -366,9 +366,12 @@ write_kernel(StoreView v, const uint16_t* key, const uint16_t* value, int64_t ks
 // ---------------------------------------------------------------------------
 struct EncodeShared {
   __align__(16) uint8_t var[kVarCap];
-  // Per high byte: low nibble = 3-bit primary code (7 = escape), high nibble =
-  // escape nibble (rank - 7, or 15 for a byte outside the table).
-  __align__(16) uint8_t composite[256];
+  // Per byte position k of a packed word and per high byte: .x = the 3-bit
+  // primary code (7 = escape) already at nibble k, .y = the escape nibble
+  // (rank - 7, or 15 for a byte outside the table) already at byte k.  Four
+  // look-ups OR into the packed codes and the escape bytes of four scalars
+  // with no shifting or repacking afterwards.
+  __align__(16) uint2 classes[4][256];
   // Per 8-bit flag mask: byte selectors (prmt nibbles) listing the flagged
   // positions in ascending order; unused selectors are 0.
   uint32_t compact[256];
@@ -377,21 +380,24 @@ struct EncodeShared {
   int raw;
 };
 
-// The composite table is indexed by the high byte rotated left by one bit: the
-// sign moves to bit 0, so +x and -x, and neighbouring exponents, share a 4-byte
-// word.  Real KV uses a handful of exponents with both signs; unrotated, +x and
-// -x sit 128 bytes apart - same bank, different word - and the look-ups of a
-// warp replay on bank conflicts.
+// The class tables are indexed by the high byte rotated left by one bit: the
+// sign moves to bit 0, so +x and -x, and neighbouring exponents, are
+// neighbours.  Real KV uses a handful of exponents with both signs; unrotated,
+// +x and -x sit 128 entries apart - same banks, different words - and the
+// look-ups of a warp replay on bank conflicts.
 __device__ __forceinline__ uint32_t table_slot(uint32_t high) {
   return ((high << 1) | (high >> 7)) & 0xffu;
 }
 
-// Fills the composite table from `rank_of` (one entry per thread).
-__device__ __forceinline__ void load_composite(EncodeShared& sh, const uint8_t* rank_of, int tid) {
+// Fills the class tables from `rank_of` and the selector table (one entry of
+// each per thread).
+__device__ __forceinline__ void load_classes(EncodeShared& sh, const uint8_t* rank_of, int tid) {
   const uint32_t r = rank_of[tid];
   const uint32_t code = min(r, (uint32_t)kPrimaryDirect);
   const uint32_t nib = r < kPrimaryDirect ? 0u : (r < kTableEntries ? r - kPrimaryDirect : 15u);
-  sh.composite[table_slot((uint32_t)tid)] = (uint8_t)(code | (nib << 4));
+#pragma unroll
+  for (int k = 0; k < 4; ++k)
+    sh.classes[k][table_slot((uint32_t)tid)] = make_uint2(code << (4 * k), nib << (8 * k));
   uint32_t pick = 0;
   int k = 0;
   for (int pos = 0; pos < 8; ++pos)
@@ -404,13 +410,14 @@ struct EncodePlan {
   bool codes;    // false: raw fallback (attn_page.py:200-202)
 };
 
-// Composite bytes of the four high bytes packed in `hi`.
-__device__ __forceinline__ uint32_t composite4(const EncodeShared& sh, uint32_t hi) {
+// Classes of the four high bytes packed in `hi`: .x = their primary codes as
+// four nibbles, .y = their escape nibbles as four bytes.
+__device__ __forceinline__ uint2 classes4(const EncodeShared& sh, uint32_t hi) {
   // All four bytes rotated at once (see table_slot).
   const uint32_t at = ((hi << 1) & 0xfefefefeu) | ((hi >> 7) & 0x01010101u);
-  const uint32_t c0 = sh.composite[at & 0xffu], c1 = sh.composite[(at >> 8) & 0xffu];
-  const uint32_t c2 = sh.composite[(at >> 16) & 0xffu], c3 = sh.composite[at >> 24];
-  return c0 | (c1 << 8) | (c2 << 16) | (c3 << 24);
+  const uint2 c0 = sh.classes[0][at & 0xffu], c1 = sh.classes[1][(at >> 8) & 0xffu];
+  const uint2 c2 = sh.classes[2][(at >> 16) & 0xffu], c3 = sh.classes[3][at >> 24];
+  return make_uint2(c0.x | c1.x | c2.x | c3.x, c0.y | c1.y | c2.y | c3.y);
 }
 
 // Low nibbles of four bytes -> four adjacent nibbles (16 bits).
@@ -440,8 +447,8 @@ __device__ __forceinline__ void encode_cta(const uint4 (&wd)[8], EncodeShared& s
   for (int st = 0; st < 8; ++st) {
     const uint32_t hi_a = __byte_perm(wd[st].x, wd[st].y, 0x7531);
     const uint32_t hi_b = __byte_perm(wd[st].z, wd[st].w, 0x7531);
-    const uint32_t ca = composite4(sh, hi_a), cb = composite4(sh, hi_b);
-    codes[st] = low_nibbles(ca) | (low_nibbles(cb) << 16);
+    const uint2 ca = classes4(sh, hi_a), cb = classes4(sh, hi_b);
+    codes[st] = ca.x | (cb.x << 16);
     const uint32_t f = (codes[st] + 0x11111111u) & 0x88888888u;  // nibbles equal to 7
     // This word's escape nibbles, in order, without a loop over them (lanes
     // differ in how many they have; a loop runs as long as the worst lane).
@@ -450,8 +457,7 @@ __device__ __forceinline__ void encode_cta(const uint4 (&wd)[8], EncodeShared& s
     const uint32_t gathered = (f >> 3) * 0x1248u;
     const uint32_t mask8 = ((gathered >> 12) & 0xfu) | ((gathered >> 24) & 0xf0u);
     const uint32_t pick = sh.compact[mask8];  // byte selectors that move flagged bytes to the front
-    const uint32_t ea = (ca >> 4) & 0x0f0f0f0fu, eb = (cb >> 4) & 0x0f0f0f0fu;
-    const uint32_t front_lo = __byte_perm(ea, eb, pick), front_hi = __byte_perm(ea, eb, pick >> 16);
+    const uint32_t front_lo = __byte_perm(ca.y, cb.y, pick), front_hi = __byte_perm(ca.y, cb.y, pick >> 16);
     const int here = __popc(f);
     uint32_t packed = low_nibbles(front_lo) | (low_nibbles(front_hi) << 16);
     packed &= here >= 8 ? 0xffffffffu : (1u << (4 * here)) - 1u;  // drop what the padding selected
@@ -544,9 +550,9 @@ __device__ __forceinline__ void encode_cta(const uint4 (&wd)[8], EncodeShared& s
 #pragma unroll
       for (int e = 0; e < 8; ++e) {
         const uint32_t high = (highs[e >> 2] >> (8 * (e & 3))) & 0xffu;
-        const uint32_t c = sh.composite[table_slot(high)];
-        if ((c & 7u) == (uint32_t)kPrimaryDirect) {
-          const uint32_t nib = c >> 4;
+        const uint2 c = sh.classes[0][table_slot(high)];
+        if (c.x == (uint32_t)kPrimaryDirect) {
+          const uint32_t nib = c.y;
           if (n_esc > 16) {
             const int bit = 8 * kHeaderBytes + 4 * ordinal;
             atomicOr(&var32[bit >> 5], nib << (bit & 31));
@@ -607,7 +613,7 @@ encode_kernel(StoreView v, int layer, uint8_t* arena, int64_t page_bytes, const 
   const int block = s.close_list[blockIdx.x];
   uint8_t* src = v.staging(s.wslot[block], layer, rec);
   const int64_t idx = v.table_index(layer, block, rec);
-  load_composite(sh, rank_of + ((int64_t)layer * 2 * s.H + rec) * 256, tid);
+  load_classes(sh, rank_of + ((int64_t)layer * 2 * s.H + rec) * 256, tid);
   uint4 wd[8];
 #pragma unroll
   for (int st = 0; st < 8; ++st) wd[st] = reinterpret_cast<const uint4*>(src)[st * kOwners + tid];
@@ -751,7 +757,7 @@ encode_records_kernel(const uint8_t* raw, const uint8_t* rank_of, const int32_t*
   const int64_t i = blockIdx.x;
   const int tid = threadIdx.x;
   const int which = kv[i];
-  load_composite(sh, rank_of + (int64_t)(table_index ? table_index[i] : (int32_t)i) * 256, tid);
+  load_classes(sh, rank_of + (int64_t)(table_index ? table_index[i] : (int32_t)i) * 256, tid);
   tile_load(tile, raw + i * kRawRecord, 256, tid);
   __syncthreads();
   uint4 wd[8];
