@@ -420,13 +420,6 @@ __device__ __forceinline__ uint2 classes4(const EncodeShared& sh, uint32_t hi) {
   return make_uint2(c0.x | c1.x | c2.x | c3.x, c0.y | c1.y | c2.y | c3.y);
 }
 
-// Low nibbles of four bytes -> four adjacent nibbles (16 bits).
-__device__ __forceinline__ uint32_t low_nibbles(uint32_t c) {
-  uint32_t t = c & 0x0f0f0f0fu;
-  t = (t | (t >> 4)) & 0x00ff00ffu;
-  return (t | (t >> 8)) & 0xffffu;
-}
-
 // `place(plan, raw)` runs on thread 0 only and returns where the record goes;
 // it sets `raw` when the record must be stored raw (it does not code, or it
 // codes but no longer fits its page); a null destination drops the record.
@@ -459,8 +452,12 @@ __device__ __forceinline__ void encode_cta(const uint4 (&wd)[8], EncodeShared& s
     const uint32_t pick = sh.compact[mask8];  // byte selectors that move flagged bytes to the front
     const uint32_t front_lo = __byte_perm(ca.y, cb.y, pick), front_hi = __byte_perm(ca.y, cb.y, pick >> 16);
     const int here = __popc(f);
-    uint32_t packed = low_nibbles(front_lo) | (low_nibbles(front_hi) << 16);
-    packed &= here >= 8 ? 0xffffffffu : (1u << (4 * here)) - 1u;  // drop what the padding selected
+    // Eight bytes holding one nibble each -> eight adjacent nibbles: OR-ing a
+    // word with itself shifted by four pairs the nibbles up in bytes 0 and 2.
+    const uint32_t pair_lo = front_lo | (front_lo >> 4), pair_hi = front_hi | (front_hi >> 4);
+    uint32_t packed = __byte_perm(pair_lo, pair_hi, 0x6420);
+    // Drop what the padding selected (a shift count of 32 gives 0).
+    packed &= __funnelshift_rc(0xffffffffu, 0u, 32 - 4 * here);
     if (n_esc < 16) queue |= (uint64_t)packed << (4 * n_esc);
     // Raw scalars (nibble 15) are rare.
     uint32_t raws = packed & (packed >> 1);
