@@ -45,7 +45,11 @@ constexpr int kPlanThreads = 256;
 struct SlotDesc {
   int64_t addr;  // global address of the record (used for raw records)
   int32_t vlen;  // rec_len: bytes past the dense part; > kVarCap marks raw
-  int32_t pad;
+  // Dynamic schedule only: the work item the record belongs to (-1: no more
+  // items for this CTA) as the producer resolved it, so that the consumers
+  // need no dependent global loads of their own at the start of an item.
+  int32_t item;
+  int32_t seq_index, first_page, pages, seq_len;
 };
 
 struct Smem {
@@ -82,6 +86,7 @@ struct DecodeParams {
   float* opart;
   float* ml;
   int32_t* status;
+  int32_t* dyn;       // dynamic schedule words of the plan (see plan_words)
   int64_t q_stride;   // in 32-bit words
   int64_t bt_stride;  // in entries
   int kvh, group, units;
@@ -92,8 +97,18 @@ struct DecodeParams {
 // Plan (int32): [0] pages per chunk, [1] units in use, [2 + 2u] sequence and
 // [3 + 2u] first page of unit u (sequence -1: idle), [2 + 2 units + 2 b] first
 // unit and [.. + 1] chunk count of sequence b, then one spare word and the
-// status word.
-__host__ __device__ __forceinline__ int64_t plan_words(int units) { return 2 + 4LL * units + 2; }
+// status word, then the words of the dynamic item schedule (batches with more
+// (sequence, head) pairs than resident CTAs): the number of attention CTAs
+// started since the plan was made, and one item counter per attention launch
+// since then.  The planner zeroes them; CTAs of one launch are all counted
+// before any CTA of the next (a dependent grid launches only when every CTA of
+// its predecessor has allowed it, which they do after being counted), so a
+// CTA's arrival number divided by the grid size is its launch's index.
+constexpr int kMaxPlanLaunches = 256;  // launches per plan that are scheduled dynamically
+constexpr int kDynWords = 4 + kMaxPlanLaunches;
+__host__ __device__ __forceinline__ int64_t status_index(int units) { return 2 + 4LL * units + 1; }
+__host__ __device__ __forceinline__ int64_t dyn_index(int units) { return status_index(units) + 1; }
+__host__ __device__ __forceinline__ int64_t plan_words(int units) { return dyn_index(units) + kDynWords; }
 
 __device__ __forceinline__ void consumer_barrier() {
   asm volatile("bar.sync 1, %0;" ::"n"(kConsumers) : "memory");
@@ -137,6 +152,10 @@ __device__ __forceinline__ bool load_item(const DecodeParams& p, int item, Item&
 // ---------------------------------------------------------------------------
 // Producer warp
 // ---------------------------------------------------------------------------
+// kDynamic: items beyond the CTA's first come first come, first served from
+// the launch's counter in the plan (CTAs that share an SM, or that got shorter
+// items, come back sooner) and every record's descriptor names its item.
+template <bool kDynamic>
 __device__ __forceinline__ void produce(const DecodeParams& p, Smem& sm) {
   const int lane = threadIdx.x & 31;
   volatile int* abort = &sm.abort;
@@ -147,9 +166,43 @@ __device__ __forceinline__ void produce(const DecodeParams& p, Smem& sm) {
   // can immediately precede this one, so they stream at once; a sequence's last
   // page (the open block the token writer and the encoder touch) waits.
   bool synced = false;
-  for (int item = blockIdx.x; item < n_items; item += gridDim.x) {
+  // Dynamic schedule.  The CTA's first item is its block index; later ones come
+  // from the counter of this launch, which the CTA's arrival number selects
+  // (past kMaxPlanLaunches launches per plan the static stride takes over).
+  // The arrival is counted before this warp allows dependent grids to launch,
+  // so that every CTA of a launch is counted before a CTA of the next one is;
+  // its result is first needed when the first record is on its way.  The next
+  // item is requested just before this one's last record is issued: late enough
+  // that a CTA does not hoard an item it will not reach for a while, early
+  // enough that the atomic's round trip hides behind the records in the ring.
+  int arrival = 0;
+  if (kDynamic && lane == 0) arrival = atomicAdd(&p.dyn[0], 1);
+  bool counted = false;
+  int launch = -1, turn = 0;
+  auto count_arrival = [&] {
+    if (!kDynamic || counted) return;
+    launch = __shfl_sync(0xffffffffu, arrival, 0) / (int)gridDim.x;
+    if (launch >= kMaxPlanLaunches) launch = -1;
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    counted = true;
+  };
+  auto take = [&]() -> int {
+    count_arrival();
+    ++turn;
+    if (!kDynamic || launch < 0) return blockIdx.x + turn * gridDim.x;
+    int item = 0;
+    if (lane == 0) item = atomicAdd(p.dyn + 4 + launch, 1);
+    return __shfl_sync(0xffffffffu, item, 0) + gridDim.x;
+  };
+  int upcoming = blockIdx.x;
+  while (upcoming < n_items) {
+    const int item = upcoming;
+    if (!kDynamic) upcoming = take();
     Item it;
-    if (!load_item(p, item, it)) continue;
+    if (!load_item(p, item, it)) {
+      if (kDynamic) upcoming = take();
+      continue;
+    }
     const int32_t* bt = p.block_table + (int64_t)it.seq_index * p.bt_stride + it.first_page;
     const int last_page = ((it.seq_len + 127) >> 7) - 1;
     for (int base = 0; base < it.pages; base += 32) {
@@ -169,6 +222,7 @@ __device__ __forceinline__ void produce(const DecodeParams& p, Smem& sm) {
       }
       const int count = min(32, it.pages - base);
       for (int j = 0; j < 2 * count; ++j) {
+        if (kDynamic && base + 32 >= it.pages && j == 2 * count - 1) upcoming = take();
         const int src = j >> 1;
         const int64_t addr = __shfl_sync(0xffffffffu, (j & 1) ? addr_v : addr_k, src);
         const int32_t vlen = __shfl_sync(0xffffffffu, (j & 1) ? len_v : len_k, src);
@@ -179,6 +233,13 @@ __device__ __forceinline__ void produce(const DecodeParams& p, Smem& sm) {
           if (ok) {
             sm.desc[slot].addr = addr;
             sm.desc[slot].vlen = vlen;
+            if (kDynamic) {
+              sm.desc[slot].item = item;
+              sm.desc[slot].seq_index = it.seq_index;
+              sm.desc[slot].first_page = it.first_page;
+              sm.desc[slot].pages = it.pages;
+              sm.desc[slot].seq_len = it.seq_len;
+            }
             if (vlen > kVarCap || vlen < kHeaderBytes) {
               // Raw records are read in place by the consumers; warm the L2.
               prefetch_l2(reinterpret_cast<const void*>(addr), kRawRecord);
@@ -194,6 +255,20 @@ __device__ __forceinline__ void produce(const DecodeParams& p, Smem& sm) {
         ++r;
         __syncwarp();
         if (*abort) return;  // uniform: lane 0's write is ordered by the warp sync
+        count_arrival();     // first record on its way: the count has long returned
+      }
+    }
+  }
+  if (kDynamic) {
+    count_arrival();
+    // End marker: the consumers learn from the ring that nothing follows.
+    if (lane == 0) {
+      const uint32_t slot = r % kSlots, use = r / kSlots;
+      bool ok = true;
+      if (use > 0) ok = bounded_wait(&sm.empty[slot], (use - 1) & 1, abort, p.status);
+      if (ok) {
+        sm.desc[slot].item = -1;
+        mbar_arrive(&sm.full[slot]);
       }
     }
   }
@@ -202,6 +277,7 @@ __device__ __forceinline__ void produce(const DecodeParams& p, Smem& sm) {
 // ---------------------------------------------------------------------------
 // Consumer warps
 // ---------------------------------------------------------------------------
+template <bool kDynamic>
 __device__ __forceinline__ void consume(const DecodeParams& p, Smem& sm) {
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int g = lane >> 2, c = lane & 3;
@@ -216,9 +292,24 @@ __device__ __forceinline__ void consume(const DecodeParams& p, Smem& sm) {
     if (lane == 0) mbar_arrive(&sm.empty[slot]);
   };
 
-  for (int item = blockIdx.x; item < n_items; item += gridDim.x) {
+  for (int item = blockIdx.x;; item += gridDim.x) {
     Item it;
-    if (!load_item(p, item, it)) continue;
+    if (kDynamic) {
+      // The first record of the next item (or the end marker) names the item.
+      const uint32_t head_slot = r % kSlots;
+      if (!bounded_wait(&sm.full[head_slot], (r / kSlots) & 1, abort, p.status)) break;
+      const SlotDesc& d = sm.desc[head_slot];
+      if (d.item < 0) break;
+      it.unit = d.item / p.kvh;
+      it.head = d.item - it.unit * p.kvh;
+      it.seq_index = d.seq_index;
+      it.first_page = d.first_page;
+      it.pages = d.pages;
+      it.seq_len = d.seq_len;
+    } else {
+      if (item >= n_items) break;
+      if (!load_item(p, item, it)) continue;
+    }
     if (!synced) {
       // Queries come from, and partial results may still be read by, the
       // preceding grids: wait for them here, after the plan lookup, while the
@@ -402,6 +493,7 @@ __device__ __forceinline__ void consume(const DecodeParams& p, Smem& sm) {
   }
 }
 
+template <bool kDynamic>
 __global__ void __launch_bounds__(kThreads, 2) decode_attn_kernel(DecodeParams p) {
   extern __shared__ __align__(128) uint8_t dyn[];
   Smem& sm = *reinterpret_cast<Smem*>(dyn);
@@ -417,11 +509,14 @@ __global__ void __launch_bounds__(kThreads, 2) decode_attn_kernel(DecodeParams p
   // Prologue done (barriers initialised).  Each role waits for the preceding
   // grid where it first needs it (see produce / consume).  The merge kernel may
   // become resident now; it waits for this grid to complete before it reads.
-  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  // (With the dynamic schedule the producer warp allows it only after its
+  // arrival has been counted, see produce.)
   if (threadIdx.x >= kConsumers) {
-    produce(p, sm);
+    if (!kDynamic) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    produce<kDynamic>(p, sm);
   } else {
-    consume(p, sm);
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    consume<kDynamic>(p, sm);
   }
   // Nothing may still be writing this CTA's shared memory when it exits: on
   // the normal path every issued copy has been consumed; after a timeout give
@@ -883,7 +978,8 @@ __device__ __forceinline__ int block_reduce_max(int v, int* scratch) {
 }
 
 __global__ void __launch_bounds__(kPlanThreads)
-plan_kernel(const int32_t* seq_lens, int32_t* plan, int batch, int units, int kvh, int slots) {
+plan_kernel(const int32_t* seq_lens, int32_t* plan, int batch, int units, int kvh, int slots,
+            int dynamic) {
   __shared__ int scratch[kPlanThreads / 32];
   __shared__ unsigned long long best;
   __shared__ int warp_total[kPlanThreads / 32];
@@ -916,10 +1012,16 @@ plan_kernel(const int32_t* seq_lens, int32_t* plan, int batch, int units, int kv
       chunks += q;
     }
     if (chunks <= capacity) {
+      // Costs in quarter pages.  Per item: ppc pages plus about three quarters
+      // of a page of start-up.  Static schedule: every CTA runs `rounds` items.
+      // Dynamic schedule with more items than CTAs: items are taken first come,
+      // first served, so the step ends within one item of the even share.
       const long long items = (long long)chunks * kvh;
       const long long rounds = max(1LL, (items + slots - 1) / slots);
-      // Per item: ppc pages plus about three quarters of a page of start-up.
-      const unsigned long long cost = (unsigned long long)(rounds * (4LL * ppc + 3));
+      const long long one = 4LL * ppc + 3;
+      const long long share = (4LL * total * kvh + 3 * items + slots - 1) / slots;
+      const unsigned long long cost =
+          (unsigned long long)(dynamic && items > slots ? share + one : rounds * one);
       // Ties go to the longer chunk (fewer partial results).
       atomicMin(&best, (cost << 20) | (unsigned long long)(0xfffff - ppc));
     }
@@ -956,9 +1058,10 @@ plan_kernel(const int32_t* seq_lens, int32_t* plan, int batch, int units, int kv
   if (tid == 0) {
     plan[0] = ppc;
     plan[1] = used;
-    plan[plan_words(units) - 2] = 0;
-    plan[plan_words(units) - 1] = 0;  // status
+    plan[status_index(units) - 1] = 0;
+    plan[status_index(units)] = 0;
   }
+  for (int i = tid; i < kDynWords; i += kPlanThreads) plan[dyn_index(units) + i] = 0;
 }
 
 int device_sms() {
@@ -1041,8 +1144,14 @@ int launch_decode(bool plain, const fp_peers* peers, int buffer, const void* q, 
   const int sms = num_sms > 0 ? num_sms : device_sms();
   const int slots = 2 * sms;
   cudaStream_t st = (cudaStream_t)stream;
+  // More (sequence, head) pairs than resident CTAs: CTAs run several items, of
+  // ragged sizes in a ragged batch, and taking them first come, first served
+  // pays; with fewer pairs every CTA has at most one item either way.  The rule
+  // depends on the call's shape only, so all layers of a step agree.
+  const bool dynamic = !plain && (long long)batch * kv_heads > slots;
   if (replan) {
-    plan_kernel<<<1, kPlanThreads, 0, st>>>(seq_lens, plan, batch, units, kv_heads, slots);
+    plan_kernel<<<1, kPlanThreads, 0, st>>>(seq_lens, plan, batch, units, kv_heads, slots,
+                                            dynamic ? 1 : 0);
     FP_LAUNCH_CHECK("plan_kernel");
   }
   DecodeParams p;
@@ -1056,7 +1165,8 @@ int launch_decode(bool plain, const fp_peers* peers, int buffer, const void* q, 
   p.plan = plan;
   p.opart = opart;
   p.ml = ml;
-  p.status = plan + plan_words(units) - 1;
+  p.status = plan + status_index(units);
+  p.dyn = plan + dyn_index(units);
   p.q_stride = q_stride / 2;
   p.bt_stride = bt_stride;
   p.kvh = kv_heads;
@@ -1064,7 +1174,8 @@ int launch_decode(bool plain, const fp_peers* peers, int buffer, const void* q, 
   p.units = units;
   p.scale_log2 = scale * 1.4426950408889634f;
   p.k = pipe_consts();
-  void (*kernel)(DecodeParams) = plain ? plain_attn_kernel : decode_attn_kernel;
+  void (*kernel)(DecodeParams) =
+      plain ? plain_attn_kernel : dynamic ? decode_attn_kernel<true> : decode_attn_kernel<false>;
   const char* name = plain ? "plain_attn_kernel" : "decode_attn_kernel";
   const int smem = plain ? (int)sizeof(PlainSmem) : (int)sizeof(Smem);
   if (int rc = cuda_status(
@@ -1191,7 +1302,8 @@ constexpr int kStaticUnitHeads = 4096;  // largest kv_heads * units served
 constexpr int kStaticUnits = 4096;      // largest units served
 constexpr size_t kStaticOpartBytes = (size_t)kStaticUnitHeads * 8 * 128 * sizeof(float);
 constexpr size_t kStaticMlBytes = (size_t)kStaticUnitHeads * 8 * 2 * sizeof(float);
-constexpr size_t kStaticPlanBytes = ((2 + 4 * (size_t)kStaticUnits + 2) * sizeof(int32_t) + 255) / 256 * 256;
+constexpr size_t kStaticPlanBytes =
+    ((2 + 4 * (size_t)kStaticUnits + 2 + kDynWords) * sizeof(int32_t) + 255) / 256 * 256;
 constexpr size_t kStaticScratchBytes = kStaticOpartBytes + kStaticMlBytes + kStaticPlanBytes;
 
 // In host code this name is only a handle for cudaGetSymbolAddress; it is not

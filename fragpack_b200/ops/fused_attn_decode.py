@@ -37,6 +37,9 @@ GQA = 8
 # Split capacity reserved per KV head, in waves of resident CTAs.
 SPLIT_WAVES = 8
 # Bits of the status word (include/fragpack_b200.h).
+# Words of the dynamic item schedule at the end of the plan (started CTAs, one
+# item counter per attention launch since the plan was made).
+_PLAN_SCHEDULE_WORDS = 4 + 256
 DECODE_WAIT_TIMEOUT = 1
 DECODE_NOT_PLAIN = 2
 
@@ -92,7 +95,7 @@ def workspace_elems(kv_heads: int, units: int) -> tuple[int, int, int]:
         Float elements of ``opart`` and ``ml``, int32 elements of ``plan``.
     """
     rows = kv_heads * units * GQA
-    return rows * 128, rows * 2, 2 + 4 * units + 2
+    return rows * 128, rows * 2, 2 + 4 * units + 2 + _PLAN_SCHEDULE_WORDS
 
 
 @functools.cache
