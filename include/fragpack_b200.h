@@ -107,7 +107,9 @@ int fp_decode_workspace(int32_t kv_heads, int32_t units, int64_t* opart_elems, i
  *   group        query heads per KV head: 1, 2, 4 or 8
  *   units        work-unit capacity per KV head, >= B
  *   replan       nonzero: recompute the plan from seq_lens (first layer of a step)
- * The last int32 of `plan` (index 2 + 4 * units + 1) is a status word: the
+ * `plan` holds 2 + 4 * units + 2 + 260 int32 (fp_decode_workspace gives the
+ * count): the reference's plan, a spare word, a status word and the words of
+ * the dynamic item schedule.  The int32 at index 2 + 4 * units + 1 is the status word: the
  * kernels OR FP_DECODE_* bits into it when a bounded device-side wait ran out
  * (results are then invalid); the planner clears it.  opart must be 16-byte
  * aligned, ml and plan 8-byte aligned.
