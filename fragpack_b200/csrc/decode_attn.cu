@@ -985,15 +985,20 @@ plan_kernel(const int32_t* seq_lens, int32_t* plan, int batch, int units, int kv
   __shared__ int warp_total[kPlanThreads / 32];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   int total = 0, longest = 0, active = 0;
+  int short_gap = 0;  // (1 << 30) - pages of the shortest sequence with context (0: none yet)
   for (int b = tid; b < batch; b += kPlanThreads) {
     const int n = (seq_lens[b] + 127) >> 7;
     total += n;
     longest = max(longest, n);
+    if (n > 0) short_gap = max(short_gap, (1 << 30) - n);
     active += n > 0;
   }
   total = block_reduce_sum(total, scratch);
   longest = block_reduce_max(longest, scratch);
+  short_gap = block_reduce_max(short_gap, scratch);
   active = block_reduce_sum(active, scratch);
+  // Sequences of one length cut into equal items: rounds of items, whoever takes them.
+  const bool ragged = short_gap > 0 && (1 << 30) - short_gap != longest;
   // Each padding row gives back the unit reserved for it.
   const int capacity = max(1, units - batch + active);
   if (tid == 0) best = ~0ull;
@@ -1013,15 +1018,15 @@ plan_kernel(const int32_t* seq_lens, int32_t* plan, int batch, int units, int kv
     }
     if (chunks <= capacity) {
       // Costs in quarter pages.  Per item: ppc pages plus about three quarters
-      // of a page of start-up.  Static schedule: every CTA runs `rounds` items.
-      // Dynamic schedule with more items than CTAs: items are taken first come,
-      // first served, so the step ends within one item of the even share.
+      // of a page of start-up.  Equal items, or a static schedule: every CTA
+      // runs `rounds` items.  Ragged items taken first come, first served: the
+      // step ends within one item of the even share.
       const long long items = (long long)chunks * kvh;
       const long long rounds = max(1LL, (items + slots - 1) / slots);
       const long long one = 4LL * ppc + 3;
       const long long share = (4LL * total * kvh + 3 * items + slots - 1) / slots;
       const unsigned long long cost =
-          (unsigned long long)(dynamic && items > slots ? share + one : rounds * one);
+          (unsigned long long)(dynamic && ragged && items > slots ? share + one : rounds * one);
       // Ties go to the longer chunk (fewer partial results).
       atomicMin(&best, (cost << 20) | (unsigned long long)(0xfffff - ppc));
     }
