@@ -546,21 +546,48 @@ struct PlainSmem {
   float mrow[8];
   __align__(16) uint2 qfrag[8][32];
   int raw[kSlots];
+  SlotDesc desc[kSlots];  // the item fields only (dynamic schedule)
   __align__(8) uint64_t full[kSlots];
   __align__(8) uint64_t empty[kSlots];
   int abort;
 };
 static_assert(sizeof(PlainSmem) <= (228 * 1024) / 2 - 1024, "PlainSmem too large for two CTAs per SM");
 
+template <bool kDynamic>
 __device__ __forceinline__ void plain_produce(const DecodeParams& p, PlainSmem& sm) {
   const int lane = threadIdx.x & 31;
   volatile int* abort = &sm.abort;
   const int n_items = p.plan[1] * p.kvh;
   uint32_t r = 0;
-  bool synced = false;  // see produce()
-  for (int item = blockIdx.x; item < n_items; item += gridDim.x) {
+  bool synced = false;  // see produce(), also for the dynamic schedule below
+  int arrival = 0;
+  if (kDynamic && lane == 0) arrival = atomicAdd(&p.dyn[0], 1);
+  bool counted = false;
+  int launch = -1, turn = 0;
+  auto count_arrival = [&] {
+    if (!kDynamic || counted) return;
+    launch = __shfl_sync(0xffffffffu, arrival, 0) / (int)gridDim.x;
+    if (launch >= kMaxPlanLaunches) launch = -1;
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    counted = true;
+  };
+  auto take = [&]() -> int {
+    count_arrival();
+    ++turn;
+    if (!kDynamic || launch < 0) return blockIdx.x + turn * gridDim.x;
+    int item = 0;
+    if (lane == 0) item = atomicAdd(p.dyn + 4 + launch, 1);
+    return __shfl_sync(0xffffffffu, item, 0) + gridDim.x;
+  };
+  int upcoming = blockIdx.x;
+  while (upcoming < n_items) {
+    const int item = upcoming;
+    if (!kDynamic) upcoming = take();
     Item it;
-    if (!load_item(p, item, it)) continue;
+    if (!load_item(p, item, it)) {
+      if (kDynamic) upcoming = take();
+      continue;
+    }
     const int32_t* bt = p.block_table + (int64_t)it.seq_index * p.bt_stride + it.first_page;
     const int last_page = ((it.seq_len + 127) >> 7) - 1;
     for (int base = 0; base < it.pages; base += 32) {
@@ -580,6 +607,7 @@ __device__ __forceinline__ void plain_produce(const DecodeParams& p, PlainSmem& 
       }
       const int count = min(32, it.pages - base);
       for (int j = 0; j < 2 * count; ++j) {
+        if (kDynamic && base + 32 >= it.pages && j == 2 * count - 1) upcoming = take();
         const int src = j >> 1;
         const int64_t addr = __shfl_sync(0xffffffffu, (j & 1) ? addr_v : addr_k, src);
         const int32_t vlen = __shfl_sync(0xffffffffu, (j & 1) ? len_v : len_k, src);
@@ -590,6 +618,13 @@ __device__ __forceinline__ void plain_produce(const DecodeParams& p, PlainSmem& 
           if (ok) {
             const bool raw = vlen > kVarCap;
             sm.raw[slot] = raw;
+            if (kDynamic) {
+              sm.desc[slot].item = item;
+              sm.desc[slot].seq_index = it.seq_index;
+              sm.desc[slot].first_page = it.first_page;
+              sm.desc[slot].pages = it.pages;
+              sm.desc[slot].seq_len = it.seq_len;
+            }
             if (raw) {
               mbar_expect_tx(&sm.full[slot], kRawRecord);
               bulk_load(sm.slots[slot], reinterpret_cast<const void*>(addr), kRawRecord,
@@ -603,11 +638,26 @@ __device__ __forceinline__ void plain_produce(const DecodeParams& p, PlainSmem& 
         ++r;
         __syncwarp();
         if (*abort) return;
+        count_arrival();
+      }
+    }
+  }
+  if (kDynamic) {
+    count_arrival();
+    if (lane == 0) {  // end marker
+      const uint32_t slot = r % kSlots, use = r / kSlots;
+      bool ok = true;
+      if (use > 0) ok = bounded_wait(&sm.empty[slot], (use - 1) & 1, abort, p.status);
+      if (ok) {
+        sm.desc[slot].item = -1;
+        mbar_arrive(&sm.full[slot]);
       }
     }
   }
 }
 
+
+template <bool kDynamic>
 __device__ __forceinline__ void plain_consume(const DecodeParams& p, PlainSmem& sm) {
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int g = lane >> 2, c = lane & 3;
@@ -640,9 +690,23 @@ __device__ __forceinline__ void plain_consume(const DecodeParams& p, PlainSmem& 
     }
   };
 
-  for (int item = blockIdx.x; item < n_items; item += gridDim.x) {
+  for (int item = blockIdx.x;; item += gridDim.x) {
     Item it;
-    if (!load_item(p, item, it)) continue;
+    if (kDynamic) {
+      const uint32_t head_slot = r % kSlots;
+      if (!bounded_wait(&sm.full[head_slot], (r / kSlots) & 1, abort, p.status)) break;
+      const SlotDesc& d = sm.desc[head_slot];
+      if (d.item < 0) break;
+      it.unit = d.item / p.kvh;
+      it.head = d.item - it.unit * p.kvh;
+      it.seq_index = d.seq_index;
+      it.first_page = d.first_page;
+      it.pages = d.pages;
+      it.seq_len = d.seq_len;
+    } else {
+      if (item >= n_items) break;
+      if (!load_item(p, item, it)) continue;
+    }
     if (!synced) {
       grid_dependency_wait();
       synced = true;
@@ -784,6 +848,7 @@ __device__ __forceinline__ void plain_consume(const DecodeParams& p, PlainSmem& 
   }
 }
 
+template <bool kDynamic>
 __global__ void __launch_bounds__(kThreads, 2) plain_attn_kernel(DecodeParams p) {
   extern __shared__ __align__(128) uint8_t dyn[];
   PlainSmem& sm = *reinterpret_cast<PlainSmem*>(dyn);
@@ -796,11 +861,12 @@ __global__ void __launch_bounds__(kThreads, 2) plain_attn_kernel(DecodeParams p)
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   __syncthreads();
-  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   if (threadIdx.x >= kConsumers) {
-    plain_produce(p, sm);
+    if (!kDynamic) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    plain_produce<kDynamic>(p, sm);
   } else {
-    plain_consume(p, sm);
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    plain_consume<kDynamic>(p, sm);
   }
   __syncthreads();
   if (sm.abort && threadIdx.x == 0) {
@@ -1153,7 +1219,7 @@ int launch_decode(bool plain, const fp_peers* peers, int buffer, const void* q, 
   // ragged sizes in a ragged batch, and taking them first come, first served
   // pays; with fewer pairs every CTA has at most one item either way.  The rule
   // depends on the call's shape only, so all layers of a step agree.
-  const bool dynamic = !plain && (long long)batch * kv_heads > slots;
+  const bool dynamic = (long long)batch * kv_heads > slots;
   if (replan) {
     plan_kernel<<<1, kPlanThreads, 0, st>>>(seq_lens, plan, batch, units, kv_heads, slots,
                                             dynamic ? 1 : 0);
@@ -1180,7 +1246,8 @@ int launch_decode(bool plain, const fp_peers* peers, int buffer, const void* q, 
   p.scale_log2 = scale * 1.4426950408889634f;
   p.k = pipe_consts();
   void (*kernel)(DecodeParams) =
-      plain ? plain_attn_kernel : dynamic ? decode_attn_kernel<true> : decode_attn_kernel<false>;
+      plain ? (dynamic ? plain_attn_kernel<true> : plain_attn_kernel<false>)
+            : (dynamic ? decode_attn_kernel<true> : decode_attn_kernel<false>);
   const char* name = plain ? "plain_attn_kernel" : "decode_attn_kernel";
   const int smem = plain ? (int)sizeof(PlainSmem) : (int)sizeof(Smem);
   if (int rc = cuda_status(
