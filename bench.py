@@ -337,6 +337,9 @@ def run_ours(args) -> dict:
         per_layer += cfg.batch * ((cfg.ctx_max + 127) // 128) * 2 * per * ap.RAW_RECORD_BYTES
     budget = int(args.hbm_budget_gb * 2**30)
     layers = args.layers or max(1, min(cfg.layers, budget // max(per_layer, 1)))
+    if world > 1 and layers > 2:
+        # An even count keeps the two gathered copies alternating inside a replayed graph.
+        layers -= layers % 2
     work = workloads.build_decode_workload(
         cfg, device, seed=args.seed, layers=layers, head_slice=head_slice,
         keep_layers=(0, layers - 1), plain=plain,
