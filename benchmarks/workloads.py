@@ -7,7 +7,7 @@ write, encode per layer, commit), in chunks of sequences so that staging stays
 small.  Physical blocks are assigned by a random permutation and never
 repeated, so every timed read comes from HBM.
 
-The KV values follow :mod:`fragpack_b200.synth`; tables are calibrated per
+The KV values follow :mod:`benchmarks.synth`; tables are calibrated per
 layer from 64 seeded sample pages drawn from the same distribution.
 """
 
@@ -18,7 +18,7 @@ from dataclasses import dataclass, replace
 import numpy as np
 import torch
 
-from fragpack_b200 import synth
+from benchmarks import synth
 from fragpack_b200.compression import attn_page as ap
 from fragpack_b200.compression.attn_tables import DeviceTables, device_tables
 from fragpack_b200.ops.hbm_kv import HbmKvStore, page_bytes
@@ -40,7 +40,7 @@ class Config:
             equal values give a fixed context.
         ragged: Re-draw lengths that are multiples of 128, so every sequence
             ends in an open (raw, writable) tail block.
-        heavy, junk: Contamination fractions (see :mod:`fragpack_b200.synth`).
+        heavy, junk: Contamination fractions (see :mod:`benchmarks.synth`).
     """
 
     name: str

@@ -25,7 +25,12 @@ import sys
 OUT = Path(__file__).resolve().parent / "_ref" / "fragpack_cuda"
 NAME = "fragpack_cuda"
 SOURCES = ("fragpack_ext.cpp", "fused_attn_decode.cu", "hbm_kv.cu")
-DEFAULT_REFERENCE = "/root/reference"
+
+
+def reference_root() -> Path:
+    """The reference checkout: ``$FRAGPACK_REFERENCE``, else ``reference`` beside this repository."""
+    env = os.environ.get("FRAGPACK_REFERENCE")
+    return Path(env) if env else Path(__file__).resolve().parents[2] / "reference"
 
 
 def built() -> Path | None:
@@ -41,7 +46,7 @@ def build(reference: str | None = None) -> Path | None:
         The shared object, or None when there is neither a checkout nor an
         earlier build.
     """
-    ops = Path(reference or os.environ.get("FRAGPACK_REFERENCE", DEFAULT_REFERENCE)) / "fragpack" / "ops"
+    ops = (Path(reference) if reference else reference_root()) / "fragpack" / "ops"
     if not all((ops / s).exists() for s in SOURCES):
         return built()
     newest = max((ops / s).stat().st_mtime for s in (*SOURCES, "fragpack_common.cuh"))

@@ -20,6 +20,7 @@ from __future__ import annotations
 
 import hashlib
 import json
+import os
 from pathlib import Path
 import sys
 
@@ -28,7 +29,7 @@ import numpy as np
 HERE = Path(__file__).resolve().parent
 sys.path.insert(0, str(HERE.parents[1]))
 
-from fragpack_b200 import synth  # noqa: E402
+from benchmarks import synth  # noqa: E402
 
 CFG1 = dict(seed=1001, layers=1, kv_heads=4, seqs=2, blocks=4, samples=64)
 
@@ -83,7 +84,8 @@ def small_cases() -> list[tuple[str, np.ndarray, np.ndarray | None, int]]:
 
 
 def main() -> None:
-    ref_root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    ref_root = sys.argv[1] if len(sys.argv) > 1 else os.environ.get(
+        "FRAGPACK_REFERENCE", str(Path(__file__).resolve().parents[3] / "reference"))
     sys.path.insert(0, ref_root)
     from fragpack.compression import attn_page as ap
     from fragpack.compression import attn_tables as at

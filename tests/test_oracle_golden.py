@@ -11,6 +11,7 @@ them.  The cases follow the reference's own unit tests
 from __future__ import annotations
 
 import hashlib
+import os
 import json
 from pathlib import Path
 import sys
@@ -134,17 +135,21 @@ def test_raw_record_is_the_staging_layout(golden) -> None:
     assert raw == golden["encoded"][i].tobytes()
 
 
-@pytest.mark.skipif(not Path("/root/reference/fragpack").exists(), reason="reference checkout absent")
+# The reference checkout: $FRAGPACK_REFERENCE, else `reference` beside this repository.
+REFERENCE = Path(os.environ.get("FRAGPACK_REFERENCE") or Path(__file__).resolve().parents[2] / "reference")
+
+
+@pytest.mark.skipif(not (REFERENCE / "fragpack").exists(), reason="reference checkout absent")
 def test_live_cross_check_against_reference() -> None:
     """Where the reference checkout is present, compare on fresh seeded records."""
     import importlib
 
-    sys.path.insert(0, "/root/reference")
+    sys.path.insert(0, str(REFERENCE))
     try:
         ref = importlib.import_module("fragpack.compression.attn_page")
     finally:
-        sys.path.remove("/root/reference")
-    from fragpack_b200 import synth
+        sys.path.remove(str(REFERENCE))
+    from benchmarks import synth
 
     rng = np.random.default_rng(99)
     scales = synth.channel_scales(5, 1, 2)[0]
