@@ -2,10 +2,13 @@
 
 API-compatible with the reference ``fragpack/compression/attn_page.py`` (same
 names, arguments, return types and byte format, documented there at :1-44).
-The difference is where the work runs: :func:`encode_record` and
-:func:`decode_record` call the sm_100a kernels through the C ABI
-(``fp_encode_records`` / ``fp_decode_records``) and therefore need a CUDA
-device; there is no CPU codec in this package.  Calibration and the LUT
+The difference is where the work runs: with a CUDA device
+:func:`encode_record` and :func:`decode_record` call the sm_100a kernels
+through the C ABI (``fp_encode_records`` / ``fp_decode_records``); without one
+they use the numpy codec of :mod:`fragpack_b200.compression.host_codec`, which
+gives the same bytes, so that offline tools and calibration machines work as
+they do with the reference.  (Only this offline package has a host form; the
+operators in ``fragpack_b200.ops`` have none.)  Calibration and the LUT
 builders are small host-side table manipulations and stay in numpy, as in the
 reference (they run offline or once at start-up).
 
@@ -105,7 +108,7 @@ def _device_luts(table: NDArray[np.uint8]):
 
 
 def encode_record(raw: NDArray[np.uint16], table: NDArray[np.uint8], kv: int) -> bytes:
-    """Encode one token-major ``[PAGE_TOKENS, HEAD_DIM]`` BF16 record on the GPU.
+    """Encode one token-major ``[PAGE_TOKENS, HEAD_DIM]`` BF16 record (on the GPU when there is one).
 
     Reference: ``attn_page.py:146-209``; the bytes are identical.
 
@@ -119,17 +122,19 @@ def encode_record(raw: NDArray[np.uint16], table: NDArray[np.uint8], kv: int) ->
 
     Raises:
         ValueError: If ``raw`` has the wrong size.
-        RuntimeError: If no CUDA device or kernel library is available.
+        RuntimeError: If a CUDA device is present but the kernel library is not built.
     """
     import torch
-
-    from fragpack_b200.ops.fragpack_ext import check, extension, stream_ptr
 
     values = np.ascontiguousarray(raw, dtype=np.uint16).reshape(-1)
     if values.size != RECORD_SCALARS:
         raise ValueError("record must hold PAGE_TOKENS * HEAD_DIM scalars")
     if not torch.cuda.is_available():
-        raise RuntimeError("encode_record runs on the GPU: no CUDA device is available")
+        from fragpack_b200.compression import host_codec
+
+        return host_codec.encode(values, rank_table(table), int(kv))
+    from fragpack_b200.ops.fragpack_ext import check, extension, stream_ptr
+
     dev = torch.device("cuda", torch.cuda.current_device())
     src = torch.from_numpy(values.view(np.int16).copy()).to(dev)
     rank_of = torch.from_numpy(rank_table(table)).to(dev)
@@ -147,7 +152,7 @@ def encode_record(raw: NDArray[np.uint16], table: NDArray[np.uint8], kv: int) ->
 
 
 def decode_record(record: bytes, table: NDArray[np.uint8], kv: int) -> NDArray[np.uint16]:
-    """Decode one record on the GPU (reference ``attn_page.py:212-269``).
+    """Decode one record, on the GPU when there is one (reference ``attn_page.py:212-269``).
 
     Args:
         record: Encoded record.
@@ -159,18 +164,20 @@ def decode_record(record: bytes, table: NDArray[np.uint8], kv: int) -> NDArray[n
 
     Raises:
         ValueError: If the length is not a possible record length.
-        RuntimeError: If no CUDA device or kernel library is available.
+        RuntimeError: If a CUDA device is present but the kernel library is not built.
     """
     import torch
-
-    from fragpack_b200.ops.fragpack_ext import check, extension, stream_ptr
 
     n = len(record)
     coded = DENSE_BYTES + HEADER_BYTES <= n <= DENSE_BYTES + VAR_CAP and n % 16 == 0
     if n != RAW_RECORD_BYTES and not coded:
         raise ValueError(f"{n} bytes is not a record length")
     if not torch.cuda.is_available():
-        raise RuntimeError("decode_record runs on the GPU: no CUDA device is available")
+        from fragpack_b200.compression import host_codec
+
+        return host_codec.decode(bytes(record), table, int(kv))
+    from fragpack_b200.ops.fragpack_ext import check, extension, stream_ptr
+
     dev = torch.device("cuda", torch.cuda.current_device())
     buf = torch.zeros(RAW_RECORD_BYTES, dtype=torch.uint8, device=dev)
     buf[:n] = torch.from_numpy(np.frombuffer(record, np.uint8).copy()).to(dev)

@@ -17,7 +17,7 @@ import pytest
 import torch
 
 import oracle
-from fragpack_b200 import synth, workloads
+from benchmarks import synth, workloads
 from fragpack_b200.compression import attn_page as ap
 from fragpack_b200.compression import attn_tables as at
 from fragpack_b200.ops import fused_attn_decode as fad
@@ -100,9 +100,12 @@ def test_operators_have_no_cpu_fallback() -> None:
         fad.decode_attention(torch.zeros(1, 3, 128, dtype=torch.bfloat16), tabs,
                              torch.zeros(1, 1, dtype=torch.int32),
                              torch.zeros(1, dtype=torch.int32), 1.0, 1, q, ws, True)
-    if not torch.cuda.is_available():
-        with pytest.raises(RuntimeError, match="GPU"):
-            ap.encode_record(np.zeros((128, 128), np.uint16), np.arange(22, dtype=np.uint8), 0)
+    # Only the offline compression package has a host form (tests/test_host_codec.py);
+    # the store, like the decode operator, refuses host tensors.
+    store = object.__new__(hbm_kv.HbmKvStore)
+    store.counters = torch.zeros(16, dtype=torch.int32)
+    with pytest.raises(RuntimeError, match="no CPU fallback"):
+        store._require_device()
 
 
 def test_layout_arithmetic() -> None:
