@@ -36,7 +36,16 @@ namespace {
 constexpr int kConsumerWarps = 8;
 constexpr int kConsumers = 32 * kConsumerWarps;  // 256 = fragment owners
 constexpr int kThreads = kConsumers + 32;        // + producer warp
-constexpr int kSlots = 3;
+// Resident CTAs per SM the kernels are shaped for.  Two: a three-slot record
+// ring and separate escape scratch for K and V records.  Three (more warps to
+// hide the decode's latencies, 72 registers per thread): a two-slot ring and
+// one escape scratch, which costs a barrier at the end of every page.
+#ifndef FPB_CTAS_PER_SM
+#define FPB_CTAS_PER_SM 2
+#endif
+constexpr int kCtasPerSm = FPB_CTAS_PER_SM;
+constexpr int kSlots = kCtasPerSm == 3 ? 2 : 3;
+constexpr int kEscBuffers = kCtasPerSm == 3 ? 1 : 2;
 constexpr int kSlotBytes = kCodedMax;            // raw records are read in place
 constexpr int kPRow = 80;                        // bytes per (head, c) row of P, padded
 constexpr int kPBytes = 32 * kPRow;
@@ -56,10 +65,9 @@ struct Smem {
   __align__(128) uint8_t slots[kSlots][kSlotBytes];
   // K and V records expand their escapes into separate buffers: the V decode of
   // a page and the K decode of the next one run without a barrier between them.
-  __align__(16) uint8_t esc[2][kEscBytes];
+  __align__(16) uint8_t esc[kEscBuffers][kEscBytes];
   __align__(16) uint8_t p[2][kPBytes];
   __align__(16) float ref[2][kConsumerWarps][8];
-  __align__(16) int flag[2][kConsumerWarps];
   __align__(16) float lsum[kConsumerWarps][8];
   float mrow[8];
   // Per item: Q^T B fragments in lane order and the K / V decode tables.
@@ -68,11 +76,11 @@ struct Smem {
   SlotDesc desc[kSlots];
   __align__(8) uint64_t full[kSlots];
   __align__(8) uint64_t empty[kSlots];
-  int abort;
+  WaitState wait;
 };
 
-// Two CTAs must fit one SM: 228 KB per SM, 1 KB reserved per CTA.
-static_assert(sizeof(Smem) <= (228 * 1024) / 2 - 1024, "Smem too large for two CTAs per SM");
+// kCtasPerSm CTAs must fit one SM: 228 KB per SM, 1 KB reserved per CTA.
+static_assert(sizeof(Smem) <= (228 * 1024) / kCtasPerSm - 1024, "Smem too large for the CTAs per SM");
 
 struct DecodeParams {
   const uint32_t* q;
@@ -92,6 +100,8 @@ struct DecodeParams {
   int kvh, group, units;
   float scale_log2;
   PipeConsts k;
+  long long wait_limit;   // cycle budget of every bounded wait
+  long long skip_record;  // test hook: ordinal of a record the producer leaves out (-1: none)
 };
 
 // Plan (int32): [0] pages per chunk, [1] units in use, [2 + 2u] sequence and
@@ -112,6 +122,20 @@ __host__ __device__ __forceinline__ int64_t plan_words(int units) { return dyn_i
 
 __device__ __forceinline__ void consumer_barrier() {
   asm volatile("bar.sync 1, %0;" ::"n"(kConsumers) : "memory");
+}
+
+// The consumer barrier combined with an OR over a predicate of every consumer.
+__device__ __forceinline__ bool consumer_barrier_or(bool mine) {
+  uint32_t any;
+  asm volatile(
+      "{\n\t.reg .pred p, q;\n\t"
+      "setp.ne.u32 p, %1, 0;\n\t"
+      "bar.red.or.pred q, 1, %2, p;\n\t"
+      "selp.u32 %0, 1, 0, q;\n\t}"
+      : "=r"(any)
+      : "r"((uint32_t)mine), "n"(kConsumers)
+      : "memory");
+  return any != 0;
 }
 
 // d += A B, one m16n8k16 BF16 tile with fp32 accumulation.
@@ -158,7 +182,8 @@ __device__ __forceinline__ bool load_item(const DecodeParams& p, int item, Item&
 template <bool kDynamic>
 __device__ __forceinline__ void produce(const DecodeParams& p, Smem& sm) {
   const int lane = threadIdx.x & 31;
-  volatile int* abort = &sm.abort;
+  WaitState* const wait = &sm.wait;
+  volatile int* abort = &sm.wait.abort;
   const int n_items = p.plan[1] * p.kvh;
   uint32_t r = 0;  // records issued so far
   // Under a programmatic dependent launch the preceding grid may still run.
@@ -224,13 +249,24 @@ __device__ __forceinline__ void produce(const DecodeParams& p, Smem& sm) {
       for (int j = 0; j < 2 * count; ++j) {
         if (kDynamic && base + 32 >= it.pages && j == 2 * count - 1) upcoming = take();
         const int src = j >> 1;
+#ifdef FPB_L2_AHEAD
+        // The ring holds few records; the lane that resolved a page a little
+        // further on brings its record into the L2 meanwhile, so that the copy
+        // into the slot that frees up next starts from there.
+        if (lane == src + FPB_L2_AHEAD && lane < count) {
+          const int32_t n = (j & 1) ? len_v : len_k;
+          if (n <= kVarCap && n >= kHeaderBytes)
+            prefetch_l2(reinterpret_cast<const void*>((j & 1) ? addr_v : addr_k),
+                        (uint32_t)(kDenseBytes + (n & ~15)));
+        }
+#endif
         const int64_t addr = __shfl_sync(0xffffffffu, (j & 1) ? addr_v : addr_k, src);
         const int32_t vlen = __shfl_sync(0xffffffffu, (j & 1) ? len_v : len_k, src);
         const uint32_t slot = r % kSlots, use = r / kSlots;
         if (lane == 0) {
           bool ok = true;
-          if (use > 0) ok = bounded_wait(&sm.empty[slot], (use - 1) & 1, abort, p.status);
-          if (ok) {
+          if (use > 0) ok = bounded_wait(&sm.empty[slot], (use - 1) & 1, wait);
+          if (ok && (long long)r != p.skip_record) {
             sm.desc[slot].addr = addr;
             sm.desc[slot].vlen = vlen;
             if (kDynamic) {
@@ -265,7 +301,7 @@ __device__ __forceinline__ void produce(const DecodeParams& p, Smem& sm) {
     if (lane == 0) {
       const uint32_t slot = r % kSlots, use = r / kSlots;
       bool ok = true;
-      if (use > 0) ok = bounded_wait(&sm.empty[slot], (use - 1) & 1, abort, p.status);
+      if (use > 0) ok = bounded_wait(&sm.empty[slot], (use - 1) & 1, wait);
       if (ok) {
         sm.desc[slot].item = -1;
         mbar_arrive(&sm.full[slot]);
@@ -281,10 +317,11 @@ template <bool kDynamic>
 __device__ __forceinline__ void consume(const DecodeParams& p, Smem& sm) {
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int g = lane >> 2, c = lane & 3;
-  volatile int* abort = &sm.abort;
+  WaitState* const wait = &sm.wait;
   const int n_items = p.plan[1] * p.kvh;
-  uint32_t r = 0;      // records consumed so far (matches the producer's count)
-  uint32_t pages = 0;  // pages consumed so far: parity selects the P / ref buffers
+  // Records consumed so far (matches the producer's count).  A page is a K and
+  // a V record, so bit 1 alternates per page: it selects the P / ref buffers.
+  uint32_t r = 0;
   bool synced = false;
 
   auto release = [&](uint32_t slot) {
@@ -297,9 +334,12 @@ __device__ __forceinline__ void consume(const DecodeParams& p, Smem& sm) {
     if (kDynamic) {
       // The first record of the next item (or the end marker) names the item.
       const uint32_t head_slot = r % kSlots;
-      if (!bounded_wait(&sm.full[head_slot], (r / kSlots) & 1, abort, p.status)) break;
+      const bool landed = bounded_wait(&sm.full[head_slot], (r / kSlots) & 1, wait);
       const SlotDesc& d = sm.desc[head_slot];
-      if (d.item < 0) break;
+      // All consumer warps leave together (a warp that left alone would hang
+      // the others at their next barrier): after a wait that ran out in any
+      // warp, or at the end marker, which every warp reads alike.
+      if (consumer_barrier_or(!landed || d.item < 0)) break;
       it.unit = d.item / p.kvh;
       it.head = d.item - it.unit * p.kvh;
       it.seq_index = d.seq_index;
@@ -333,21 +373,27 @@ __device__ __forceinline__ void consume(const DecodeParams& p, Smem& sm) {
     // s[2jj+e] and O[head 2c+e][dim 16w + 8jj + g] in o[2jj+e].
     float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
     float o[4] = {0.f, 0.f, 0.f, 0.f};
+    // Few values stay live across the page loop: pages to go, the sequence's
+    // tokens from the current page on, and the row of the partial result.
+    const int row0 = (it.head * p.units + it.unit) * 8;
+    int tok_left = it.seq_len - it.first_page * 128;
 
-    for (int i = 0; i < it.pages; ++i, ++pages) {
-      const int buf = pages & 1;
-      const int page_tok0 = (it.first_page + i) * 128;
+    for (int left = it.pages; left > 0; --left, tok_left -= 128) {
+      const int buf = (r >> 1) & 1;
       // ---------------- K: S^T = K Q^T
       float s[4] = {0.f, 0.f, 0.f, 0.f};
       {
         const uint32_t slot = r % kSlots;
-        bounded_wait(&sm.full[slot], (r / kSlots) & 1, abort, p.status);
+        // A record whose wait ran out contributes nothing (the status word
+        // marks the step invalid); its descriptor is not trusted either.
+        const bool landed = bounded_wait(&sm.full[slot], (r / kSlots) & 1, wait);
         const int32_t vlen = sm.desc[slot].vlen;
         auto qk = [&](int st, const uint32_t (&w)[4]) {
           const uint2 qb = sm.qfrag[st][lane];
           mma_16816(s, w[0], w[2], w[1], w[3], qb.x, qb.y);
         };
-        if (vlen > kVarCap || vlen < kHeaderBytes) {
+        if (!landed) {
+        } else if (vlen > kVarCap || vlen < kHeaderBytes) {
           const uint8_t* rec = reinterpret_cast<const uint8_t*>(sm.desc[slot].addr);
           release(slot);
           raw_record_words(rec, tid, qk);
@@ -357,12 +403,13 @@ __device__ __forceinline__ void consume(const DecodeParams& p, Smem& sm) {
         ++r;
       }
       // ---------------- softmax bookkeeping
-      const int tok = page_tok0 + 16 * warp + g;
-      const bool in0 = tok < it.seq_len, in1 = tok + 8 < it.seq_len;
-      s[0] = in0 ? s[0] * p.scale_log2 : -INFINITY;
-      s[1] = in0 ? s[1] * p.scale_log2 : -INFINITY;
-      s[2] = in1 ? s[2] * p.scale_log2 : -INFINITY;
-      s[3] = in1 ? s[3] * p.scale_log2 : -INFINITY;
+#pragma unroll
+      for (int x = 0; x < 4; ++x) s[x] *= p.scale_log2;
+      if (tok_left < 128) {  // the sequence's last page: mask its tail
+        const int tok = 16 * warp + g;
+        if (tok >= tok_left) s[0] = s[1] = -INFINITY;
+        if (tok + 8 >= tok_left) s[2] = s[3] = -INFINITY;
+      }
       float mx[2] = {fmaxf(s[0], s[2]), fmaxf(s[1], s[3])};
 #pragma unroll
       for (int x = 4; x < 32; x <<= 1) {
@@ -371,7 +418,6 @@ __device__ __forceinline__ void consume(const DecodeParams& p, Smem& sm) {
       }
       const bool raised = __any_sync(0xffffffffu, mx[0] > m_run[0] || mx[1] > m_run[1]);
       if (g == 0) *reinterpret_cast<float2*>(&sm.ref[buf][warp][2 * c]) = make_float2(mx[0], mx[1]);
-      if (lane == 0) sm.flag[buf][warp] = raised;
       // P rows: (head, c') holds, for every k-step st, the two B words
       // (tokens 16 st + 2 c' + {0,1} and + 8) of the second product.
       uint8_t* prow = sm.p[buf];
@@ -392,11 +438,9 @@ __device__ __forceinline__ void consume(const DecodeParams& p, Smem& sm) {
         for (int x = 0; x < 4; ++x) pv[x] = fast_exp2(s[x] - m_run[x & 1]);
         put_p(pv);
       }
-      consumer_barrier();
       {
-        const int4 f0 = *reinterpret_cast<const int4*>(&sm.flag[buf][0]);
-        const int4 f1 = *reinterpret_cast<const int4*>(&sm.flag[buf][4]);
-        if (f0.x | f0.y | f0.z | f0.w | f1.x | f1.y | f1.z | f1.w) {
+        // One barrier per page, carrying "some warp's maximum rose".
+        if (consumer_barrier_or(raised)) {
           // Some head's maximum rose: rescale the state, redo P against it.
           float m_new[2] = {m_run[0], m_run[1]};
 #pragma unroll
@@ -427,7 +471,7 @@ __device__ __forceinline__ void consume(const DecodeParams& p, Smem& sm) {
       // ---------------- V: O^T += V^T P^T
       {
         const uint32_t slot = r % kSlots;
-        bounded_wait(&sm.full[slot], (r / kSlots) & 1, abort, p.status);
+        const bool landed = bounded_wait(&sm.full[slot], (r / kSlots) & 1, wait);
         const int32_t vlen = sm.desc[slot].vlen;
         const uint4* pw = reinterpret_cast<const uint4*>(prow + (g * 4 + c) * kPRow);
         uint4 b;
@@ -435,10 +479,11 @@ __device__ __forceinline__ void consume(const DecodeParams& p, Smem& sm) {
           if ((st & 1) == 0) b = pw[st >> 1];
           mma_16816(o, w[0], w[2], w[1], w[3], (st & 1) ? b.z : b.x, (st & 1) ? b.w : b.y);
         };
-        if (vlen > kVarCap || vlen < kHeaderBytes) {
+        if (!landed) {
+        } else if (vlen > kVarCap || vlen < kHeaderBytes) {
           const uint8_t* rec = reinterpret_cast<const uint8_t*>(sm.desc[slot].addr);
           release(slot);
-          const int rem = it.seq_len - page_tok0;
+          const int rem = tok_left;
           if (rem < 128) {
             // An open block (always a raw record) may hold stale bytes of the
             // slot's previous owner beyond its last token: force them to zero
@@ -457,20 +502,22 @@ __device__ __forceinline__ void consume(const DecodeParams& p, Smem& sm) {
             raw_record_words(rec, tid, pv_word);
           }
         } else {
-          coded_record_words(sm.slots[slot], vlen, sm.tabs[1], sm.esc[1], tid, p.k, [&] { release(slot); },
+          coded_record_words(sm.slots[slot], vlen, sm.tabs[1], sm.esc[kEscBuffers - 1], tid, p.k, [&] { release(slot); },
                              pv_word);
         }
         ++r;
       }
+      // One escape scratch for K and V: the next page's K decode must not
+      // start expanding into it while another warp still reads this page's V.
+      if (kEscBuffers == 1) consumer_barrier();
     }
 
     // ---------------- partial result of this (unit, head)
-    const int64_t row0 = ((int64_t)it.head * p.units + it.unit) * 8;
 #pragma unroll
     for (int jj = 0; jj < 2; ++jj)
 #pragma unroll
       for (int e = 0; e < 2; ++e)
-        p.opart[(row0 + 2 * c + e) * 128 + 16 * warp + 8 * jj + g] = o[2 * jj + e];
+        p.opart[(int64_t)(row0 + 2 * c + e) * 128 + 16 * warp + 8 * jj + g] = o[2 * jj + e];
     float l[2] = {l_run[0], l_run[1]};
 #pragma unroll
     for (int x = 4; x < 32; x <<= 1) {
@@ -485,8 +532,8 @@ __device__ __forceinline__ void consume(const DecodeParams& p, Smem& sm) {
       float sum = 0.f;
 #pragma unroll
       for (int w = 0; w < kConsumerWarps; ++w) sum += sm.lsum[w][tid];
-      p.ml[(row0 + tid) * 2] = sm.mrow[tid];
-      p.ml[(row0 + tid) * 2 + 1] = sum;
+      p.ml[(int64_t)(row0 + tid) * 2] = sm.mrow[tid];
+      p.ml[(int64_t)(row0 + tid) * 2 + 1] = sum;
     }
     // The next item's first page barrier orders these reads before the next
     // writes of lsum / mrow.
@@ -494,7 +541,7 @@ __device__ __forceinline__ void consume(const DecodeParams& p, Smem& sm) {
 }
 
 template <bool kDynamic>
-__global__ void __launch_bounds__(kThreads, 2) decode_attn_kernel(DecodeParams p) {
+__global__ void __launch_bounds__(kThreads, kCtasPerSm) decode_attn_kernel(DecodeParams p) {
   extern __shared__ __align__(128) uint8_t dyn[];
   Smem& sm = *reinterpret_cast<Smem*>(dyn);
   if (threadIdx.x == 0) {
@@ -502,7 +549,9 @@ __global__ void __launch_bounds__(kThreads, 2) decode_attn_kernel(DecodeParams p
       mbar_init(&sm.full[s], 1);
       mbar_init(&sm.empty[s], kConsumerWarps);
     }
-    sm.abort = 0;
+    sm.wait.abort = 0;
+    sm.wait.status = p.status;
+    sm.wait.limit = p.wait_limit;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   __syncthreads();
@@ -515,14 +564,17 @@ __global__ void __launch_bounds__(kThreads, 2) decode_attn_kernel(DecodeParams p
     if (!kDynamic) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     produce<kDynamic>(p, sm);
   } else {
-    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    // With the dynamic schedule the producer warp alone allows dependents,
+    // after its arrival has been counted (the instruction takes effect with
+    // the first thread of the CTA that issues it).
+    if (!kDynamic) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     consume<kDynamic>(p, sm);
   }
   // Nothing may still be writing this CTA's shared memory when it exits: on
   // the normal path every issued copy has been consumed; after a timeout give
   // the copies in flight a bounded chance to land.
   __syncthreads();
-  if (sm.abort && threadIdx.x == 0) {
+  if (sm.wait.abort && threadIdx.x == 0) {
     const long long t0 = clock64();
     while (clock64() - t0 < 20000000LL) {
     }
@@ -541,7 +593,6 @@ struct PlainSmem {
   __align__(128) uint8_t slots[kSlots][kRawRecord];
   __align__(16) uint8_t p[2][kPBytes];
   __align__(16) float ref[2][kConsumerWarps][8];
-  __align__(16) int flag[2][kConsumerWarps];
   __align__(16) float lsum[kConsumerWarps][8];
   float mrow[8];
   __align__(16) uint2 qfrag[8][32];
@@ -549,14 +600,15 @@ struct PlainSmem {
   SlotDesc desc[kSlots];  // the item fields only (dynamic schedule)
   __align__(8) uint64_t full[kSlots];
   __align__(8) uint64_t empty[kSlots];
-  int abort;
+  WaitState wait;
 };
 static_assert(sizeof(PlainSmem) <= (228 * 1024) / 2 - 1024, "PlainSmem too large for two CTAs per SM");
 
 template <bool kDynamic>
 __device__ __forceinline__ void plain_produce(const DecodeParams& p, PlainSmem& sm) {
   const int lane = threadIdx.x & 31;
-  volatile int* abort = &sm.abort;
+  WaitState* const wait = &sm.wait;
+  volatile int* abort = &sm.wait.abort;
   const int n_items = p.plan[1] * p.kvh;
   uint32_t r = 0;
   bool synced = false;  // see produce(), also for the dynamic schedule below
@@ -614,7 +666,7 @@ __device__ __forceinline__ void plain_produce(const DecodeParams& p, PlainSmem& 
         const uint32_t slot = r % kSlots, use = r / kSlots;
         if (lane == 0) {
           bool ok = true;
-          if (use > 0) ok = bounded_wait(&sm.empty[slot], (use - 1) & 1, abort, p.status);
+          if (use > 0) ok = bounded_wait(&sm.empty[slot], (use - 1) & 1, wait);
           if (ok) {
             const bool raw = vlen > kVarCap;
             sm.raw[slot] = raw;
@@ -647,7 +699,7 @@ __device__ __forceinline__ void plain_produce(const DecodeParams& p, PlainSmem& 
     if (lane == 0) {  // end marker
       const uint32_t slot = r % kSlots, use = r / kSlots;
       bool ok = true;
-      if (use > 0) ok = bounded_wait(&sm.empty[slot], (use - 1) & 1, abort, p.status);
+      if (use > 0) ok = bounded_wait(&sm.empty[slot], (use - 1) & 1, wait);
       if (ok) {
         sm.desc[slot].item = -1;
         mbar_arrive(&sm.full[slot]);
@@ -661,7 +713,7 @@ template <bool kDynamic>
 __device__ __forceinline__ void plain_consume(const DecodeParams& p, PlainSmem& sm) {
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int g = lane >> 2, c = lane & 3;
-  volatile int* abort = &sm.abort;
+  WaitState* const wait = &sm.wait;
   const int n_items = p.plan[1] * p.kvh;
   uint32_t r = 0, pages = 0;
   bool synced = false;
@@ -669,9 +721,9 @@ __device__ __forceinline__ void plain_consume(const DecodeParams& p, PlainSmem& 
   // Owner words of the record in `slot` (zeros for a record that is not plain),
   // in two halves of four 16-byte words to stay inside the register budget;
   // the slot goes back to the producer once the warp has read its last word.
-  auto record_words = [&](uint32_t slot, auto&& emit) {
+  auto record_words = [&](uint32_t slot, bool landed, auto&& emit) {
     const uint4* src = reinterpret_cast<const uint4*>(sm.slots[slot]);
-    const bool raw = sm.raw[slot] != 0;
+    const bool raw = landed && sm.raw[slot] != 0;
 #pragma unroll
     for (int half = 0; half < 2; ++half) {
       uint4 v[4];
@@ -694,9 +746,12 @@ __device__ __forceinline__ void plain_consume(const DecodeParams& p, PlainSmem& 
     Item it;
     if (kDynamic) {
       const uint32_t head_slot = r % kSlots;
-      if (!bounded_wait(&sm.full[head_slot], (r / kSlots) & 1, abort, p.status)) break;
+      const bool landed = bounded_wait(&sm.full[head_slot], (r / kSlots) & 1, wait);
       const SlotDesc& d = sm.desc[head_slot];
-      if (d.item < 0) break;
+      // All consumer warps leave together (a warp that left alone would hang
+      // the others at their next barrier): after a wait that ran out in any
+      // warp, or at the end marker, which every warp reads alike.
+      if (consumer_barrier_or(!landed || d.item < 0)) break;
       it.unit = d.item / p.kvh;
       it.head = d.item - it.unit * p.kvh;
       it.seq_index = d.seq_index;
@@ -728,19 +783,20 @@ __device__ __forceinline__ void plain_consume(const DecodeParams& p, PlainSmem& 
       float s[4] = {0.f, 0.f, 0.f, 0.f};
       {
         const uint32_t slot = r % kSlots;
-        bounded_wait(&sm.full[slot], (r / kSlots) & 1, abort, p.status);
-        record_words(slot, [&](int st, const uint32_t (&w)[4]) {
+        const bool landed = bounded_wait(&sm.full[slot], (r / kSlots) & 1, wait);
+        record_words(slot, landed, [&](int st, const uint32_t (&w)[4]) {
           const uint2 qb = sm.qfrag[st][lane];
           mma_16816(s, w[0], w[2], w[1], w[3], qb.x, qb.y);
         });
         ++r;
       }
-      const int tok = page_tok0 + 16 * warp + g;
-      const bool in0 = tok < it.seq_len, in1 = tok + 8 < it.seq_len;
-      s[0] = in0 ? s[0] * p.scale_log2 : -INFINITY;
-      s[1] = in0 ? s[1] * p.scale_log2 : -INFINITY;
-      s[2] = in1 ? s[2] * p.scale_log2 : -INFINITY;
-      s[3] = in1 ? s[3] * p.scale_log2 : -INFINITY;
+#pragma unroll
+      for (int x = 0; x < 4; ++x) s[x] *= p.scale_log2;
+      if (page_tok0 + 128 > it.seq_len) {  // the sequence's last page: mask its tail
+        const int tok = page_tok0 + 16 * warp + g;
+        if (tok >= it.seq_len) s[0] = s[1] = -INFINITY;
+        if (tok + 8 >= it.seq_len) s[2] = s[3] = -INFINITY;
+      }
       float mx[2] = {fmaxf(s[0], s[2]), fmaxf(s[1], s[3])};
 #pragma unroll
       for (int x = 4; x < 32; x <<= 1) {
@@ -749,7 +805,6 @@ __device__ __forceinline__ void plain_consume(const DecodeParams& p, PlainSmem& 
       }
       const bool raised = __any_sync(0xffffffffu, mx[0] > m_run[0] || mx[1] > m_run[1]);
       if (g == 0) *reinterpret_cast<float2*>(&sm.ref[buf][warp][2 * c]) = make_float2(mx[0], mx[1]);
-      if (lane == 0) sm.flag[buf][warp] = raised;
       uint8_t* prow = sm.p[buf];
       auto put_p = [&](const float (&pv)[4]) {
 #pragma unroll
@@ -768,11 +823,9 @@ __device__ __forceinline__ void plain_consume(const DecodeParams& p, PlainSmem& 
         for (int x = 0; x < 4; ++x) pv[x] = fast_exp2(s[x] - m_run[x & 1]);
         put_p(pv);
       }
-      consumer_barrier();
       {
-        const int4 f0 = *reinterpret_cast<const int4*>(&sm.flag[buf][0]);
-        const int4 f1 = *reinterpret_cast<const int4*>(&sm.flag[buf][4]);
-        if (f0.x | f0.y | f0.z | f0.w | f1.x | f1.y | f1.z | f1.w) {
+        // One barrier per page, carrying "some warp's maximum rose".
+        if (consumer_barrier_or(raised)) {
           float m_new[2] = {m_run[0], m_run[1]};
 #pragma unroll
           for (int w = 0; w < kConsumerWarps; ++w) {
@@ -799,11 +852,11 @@ __device__ __forceinline__ void plain_consume(const DecodeParams& p, PlainSmem& 
       l_run[1] += pv[1] + pv[3];
       {
         const uint32_t slot = r % kSlots;
-        bounded_wait(&sm.full[slot], (r / kSlots) & 1, abort, p.status);
+        const bool landed = bounded_wait(&sm.full[slot], (r / kSlots) & 1, wait);
         const uint4* pw = reinterpret_cast<const uint4*>(prow + (g * 4 + c) * kPRow);
         const int rem = it.seq_len - page_tok0;
         uint4 b;
-        record_words(slot, [&](int st, const uint32_t (&w)[4]) {
+        record_words(slot, landed, [&](int st, const uint32_t (&w)[4]) {
           uint32_t a[4] = {w[0], w[1], w[2], w[3]};
           if (rem < 128) {
             // Stale bytes beyond the last token of an open block must not meet
@@ -857,7 +910,9 @@ __global__ void __launch_bounds__(kThreads, 2) plain_attn_kernel(DecodeParams p)
       mbar_init(&sm.full[s], 1);
       mbar_init(&sm.empty[s], kConsumerWarps);
     }
-    sm.abort = 0;
+    sm.wait.abort = 0;
+    sm.wait.status = p.status;
+    sm.wait.limit = p.wait_limit;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   __syncthreads();
@@ -865,11 +920,11 @@ __global__ void __launch_bounds__(kThreads, 2) plain_attn_kernel(DecodeParams p)
     if (!kDynamic) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     plain_produce<kDynamic>(p, sm);
   } else {
-    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    if (!kDynamic) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     plain_consume<kDynamic>(p, sm);
   }
   __syncthreads();
-  if (sm.abort && threadIdx.x == 0) {
+  if (sm.wait.abort && threadIdx.x == 0) {
     const long long t0 = clock64();
     while (clock64() - t0 < 20000000LL) {
     }
@@ -1135,20 +1190,21 @@ plan_kernel(const int32_t* seq_lens, int32_t* plan, int batch, int units, int kv
   for (int i = tid; i < kDynWords; i += kPlanThreads) plan[dyn_index(units) + i] = 0;
 }
 
+}  // namespace
+
 int device_sms() {
-  static int cached[64] = {0};
+  static std::atomic<int> cached[64];
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
-  if (cached[dev] == 0) {
-    int n = 0;
+  int n = cached[dev].load(std::memory_order_relaxed);
+  if (n == 0) {
     if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0)
       n = 148;
-    cached[dev] = n;
+    cached[dev].store(n, std::memory_order_relaxed);
   }
-  return cached[dev];
+  return n;
 }
 
-}  // namespace
 }  // namespace fpb
 
 using namespace fpb;
@@ -1170,6 +1226,7 @@ int launch_decode(bool plain, const fp_peers* peers, int buffer, const void* q, 
   FP_REQUIRE(group == 1 || group == 2 || group == 4 || group == 8,
              "query group %d must be 1, 2, 4 or 8", group);
   FP_REQUIRE(units >= batch, "decode needs at least one unit per sequence");
+  FP_REQUIRE((int64_t)kv_heads * units * 8 < (1LL << 31), "kv_heads * units too large");
   FP_REQUIRE(q && rec_addr && rec_len && (plain || (plut && slut)) && block_table && seq_lens &&
                  opart && ml && plan && (out || peers),
              "null decode argument");
@@ -1213,7 +1270,7 @@ int launch_decode(bool plain, const fp_peers* peers, int buffer, const void* q, 
              "out rows must be 4-byte aligned (8-byte in a peer group)");
   FP_REQUIRE(reinterpret_cast<uintptr_t>(out) % 4 == 0, "out rows must be 4-byte aligned");
   const int sms = num_sms > 0 ? num_sms : device_sms();
-  const int slots = 2 * sms;
+  const int slots = (plain ? 2 : kCtasPerSm) * sms;
   cudaStream_t st = (cudaStream_t)stream;
   // More (sequence, head) pairs than resident CTAs: CTAs run several items, of
   // ragged sizes in a ragged batch, and taking them first come, first served
@@ -1245,13 +1302,16 @@ int launch_decode(bool plain, const fp_peers* peers, int buffer, const void* q, 
   p.units = units;
   p.scale_log2 = scale * 1.4426950408889634f;
   p.k = pipe_consts();
+  p.wait_limit = wait_debug().limit;
+  p.skip_record = wait_debug().skip_record;
   void (*kernel)(DecodeParams) =
       plain ? (dynamic ? plain_attn_kernel<true> : plain_attn_kernel<false>)
             : (dynamic ? decode_attn_kernel<true> : decode_attn_kernel<false>);
   const char* name = plain ? "plain_attn_kernel" : "decode_attn_kernel";
   const int smem = plain ? (int)sizeof(PlainSmem) : (int)sizeof(Smem);
-  if (int rc = cuda_status(
-          cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem), name))
+  // The shared memory limit is set once per device and kernel, not per call.
+  static std::atomic<uint64_t> smem_allowed[4];
+  if (int rc = allow_dynamic_smem(kernel, smem, smem_allowed[(plain ? 2 : 0) + (dynamic ? 1 : 0)]))
     return rc;
   const long long max_items = (long long)units * kv_heads;
   const int grid = (int)(max_items < slots ? max_items : slots);
@@ -1385,19 +1445,21 @@ static __device__ __align__(256) uint8_t g_decode_scratch[kStaticScratchBytes];
 // Device address of g_decode_scratch on the current device, looked up once per
 // device (with that device current) and cached.
 int static_scratch(uint8_t** base) {
-  static uint8_t* cached[64] = {nullptr};
+  static std::atomic<uint8_t*> cached[64];
   int dev = 0;
   if (int rc = cuda_status(cudaGetDevice(&dev), "cudaGetDevice")) return rc;
   if (dev < 0 || dev >= 64) return fail(FP_ERR_ARGUMENT, "device index %d not supported", dev);
-  if (cached[dev] == nullptr) {
+  uint8_t* known = cached[dev].load(std::memory_order_acquire);
+  if (known == nullptr) {
     void* ptr = nullptr;
     if (int rc = cuda_status(cudaGetSymbolAddress(&ptr, g_decode_scratch),
                              "cudaGetSymbolAddress(g_decode_scratch)"))
       return rc;
     if (ptr == nullptr) return fail(FP_ERR_CUDA, "static decode scratch has no device address");
-    cached[dev] = static_cast<uint8_t*>(ptr);
+    known = static_cast<uint8_t*>(ptr);
+    cached[dev].store(known, std::memory_order_release);
   }
-  *base = cached[dev];
+  *base = known;
   return FP_OK;
 }
 

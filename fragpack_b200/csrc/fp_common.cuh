@@ -67,6 +67,17 @@ __device__ __forceinline__ uint32_t mad_lo(uint32_t a, uint32_t b, uint32_t c) {
   return r;
 }
 
+// x >> 16.  With FPB_SHIFT_MULHI the shift is a high multiply by 2^16 on the
+// multiply pipe instead of a funnel shift on the ALU pipe.
+__device__ __forceinline__ uint32_t shift_right_16(uint32_t x, const PipeConsts& k) {
+#ifdef FPB_SHIFT_MULHI
+  return mul_hi(x, k.two16);
+#else
+  (void)k;
+  return x >> 16;
+#endif
+}
+
 __device__ __forceinline__ uint32_t smem_addr(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
 }
@@ -113,7 +124,8 @@ __device__ __forceinline__ HeadTables load_tables(const int32_t* plut, const uin
                                                   int table_index) {
   HeadTables t;
   t.p0 = static_cast<uint32_t>(plut[2 * table_index]);
-  t.p1 = static_cast<uint32_t>(plut[2 * table_index + 1]);
+  // Entry 7 is the escape code: the decoder relies on it reading as 0x00.
+  t.p1 = static_cast<uint32_t>(plut[2 * table_index + 1]) & 0x00ffffffu;
   t.ext = *reinterpret_cast<const uint4*>(slut + 16 * table_index);
   return t;
 }
@@ -146,10 +158,16 @@ __device__ __forceinline__ void raw_record_words(const uint8_t* rec, int tid, Em
 // Phases: (1) the warp expands its escape nibbles through the extended table
 // into sliding windows and patches raw scalars; (2) every owner counts its
 // escapes and a warp scan gives its first ordinal; (3) per word: primary codes
-// through prmt over the 8-byte table, escape bytes picked from two windows by
-// exclusive rank and merged, low and high bytes interleaved.
+// through prmt over the 8-byte table (an escape code selects the table's zero
+// byte), escape bytes picked from two windows by exclusive rank, masked to the
+// escape positions and OR-ed in, low and high bytes interleaved.
 // The scheme is the one the format was laid out for
 // (fragpack/ops/fragpack_common.cuh:92-186).
+//
+// The integer (ALU) pipe is the busiest unit of every kernel that runs this,
+// so whatever has an equivalent on another pipe is written that way: adds as
+// multiply-adds (k.one, k.four are run-time multipliers), the per-owner escape
+// count as eight population counts, the scan's adds as predicated multiply-adds.
 // kEagerLow: fetch all low bytes up front (records read straight from global
 // memory, where four serialised fetches inside the word loop would each expose
 // the memory latency) instead of on demand (records staged in shared memory,
@@ -174,32 +192,51 @@ __device__ __forceinline__ void coded_record_words(const uint8_t* rec, int vlen,
   const uint16_t* h16 = reinterpret_cast<const uint16_t*>(var);
   const uint32_t* h32 = reinterpret_cast<const uint32_t*>(var);
   uint8_t* mine = esc + kEscPad + 64 * warp;
+  // The header holds exclusive per-warp prefixes; the last warp's range ends at
+  // the record's totals, whose low halves are h16[0] (escapes) and h16[2] (raw).
   const int first_esc = min((int)h16[8 + warp], kEscOrdinalCap);
   {
-    const int end_esc = min(warp < 7 ? (int)h16[9 + warp] : (int)h32[0], kEscOrdinalCap);
+    const int end_esc = min((int)h16[warp < 7 ? 9 + warp : 0], kEscOrdinalCap);
     const uint32_t* nibbles = reinterpret_cast<const uint32_t*>(var + kHeaderBytes);
-    // Last nibble word inside the record: lanes past the warp's range clamp to it.
-    const int last_word = max(0, (vlen - kHeaderBytes - 4) >> 2);
     const uint4 ext = tab.ext;
     __syncwarp();  // the previous record's readers of `mine` are done
     // 31 groups of eight escapes per round: lane L expands group g8 and takes
     // the first bytes of the next group from lane L + 1 (lane 31 only feeds).
+    // end_esc <= kEscOrdinalCap keeps every nibble word inside the 2048-byte
+    // variable region of a staged record; a record read in place from global
+    // memory may end sooner, so there the index is clamped to the record.
     for (int base = first_esc >> 3; 8 * base < end_esc; base += 31) {
-      const int g8 = base + lane;
-      const uint32_t n0 = nibbles[min(g8, last_word)];
+      int g8 = base + lane;
+      if (kEagerLow) g8 = min(g8, max(0, (vlen - kHeaderBytes - 4) >> 2));
+      const uint32_t n0 = nibbles[g8];
       const uint32_t b0 = extended_bytes(ext, n0), b1 = extended_bytes(ext, n0 >> 16);
       const uint32_t b2 = __shfl_down_sync(0xffffffffu, b0, 1);
-      if (lane < 31 && 8 * g8 < end_esc) {
-        uint4* dst = reinterpret_cast<uint4*>(mine + 32 * g8);
+#ifdef FPB_EXPAND_BRANCH
+      if (lane < 31 && 8 * (base + lane) < end_esc) {
+        uint4* dst = reinterpret_cast<uint4*>(mine + 32 * (base + lane));
         dst[0] = make_uint4(b0, __funnelshift_r(b0, b1, 8), __funnelshift_r(b0, b1, 16),
                             __funnelshift_r(b0, b1, 24));
         dst[1] = make_uint4(b1, __funnelshift_r(b1, b2, 8), __funnelshift_r(b1, b2, 16),
                             __funnelshift_r(b1, b2, 24));
       }
+#else
+      {
+        // Lanes with nothing to store (the feeding lane 31, groups past the
+        // warp's range) store to the spare 32 bytes at the end of the scratch
+        // instead of branching around the stores.
+        const bool live = lane < 31 && 8 * (base + lane) < end_esc;
+        uint4* dst = reinterpret_cast<uint4*>(live ? mine + 32 * (base + lane)
+                                                   : esc + kEscBytes - 32);
+        dst[0] = make_uint4(b0, __funnelshift_r(b0, b1, 8), __funnelshift_r(b0, b1, 16),
+                            __funnelshift_r(b0, b1, 24));
+        dst[1] = make_uint4(b1, __funnelshift_r(b1, b2, 8), __funnelshift_r(b1, b2, 16),
+                            __funnelshift_r(b1, b2, 24));
+      }
+#endif
     }
     // Raw scalars are rare: at most kMaxWarpRaw per warp, one patch per lane.
     const int first_raw = h16[16 + warp];
-    const int n_raw = min((warp < 7 ? (int)h16[17 + warp] : (int)h32[1]) - first_raw, kMaxWarpRaw);
+    const int n_raw = min((int)h16[warp < 7 ? 17 + warp : 2] - first_raw, kMaxWarpRaw);
     if (n_raw > 0) {  // uniform over the warp
       uint32_t patch = 0;
       if (lane < n_raw) {
@@ -215,8 +252,6 @@ __device__ __forceinline__ void coded_record_words(const uint8_t* rec, int vlen,
 #pragma unroll
         for (int j = 0; j < 4; ++j) mine[4 * (x - j) + j] = (uint8_t)(patch >> 16);
       }
-    } else {
-      __syncwarp();
     }
   }
 
@@ -234,20 +269,30 @@ __device__ __forceinline__ void coded_record_words(const uint8_t* rec, int vlen,
     // Bit 3 of the three stored words carries the fourth word, one bit each.
     sel[4 * gi + 3] =
         ((w0 >> 3) & 0x11111111u) | ((w1 >> 2) & 0x22222222u) | ((w2 >> 1) & 0x44444444u);
-  }
-  int count = 0;
 #pragma unroll
-  for (int gi = 0; gi < 2; ++gi) {
-#pragma unroll
-    for (int x = 0; x < 4; ++x)
+    for (int x = 0; x < 3; ++x)
       flag[4 * gi + x] = mad_lo(sel[4 * gi + x], k.one, 0x11111111u) & 0x88888888u;
-    // The flags of four words sit on distinct bits once shifted by 0..3.
-    count += __popc(flag[4 * gi] | (flag[4 * gi + 1] >> 1) | (flag[4 * gi + 2] >> 2) |
-                    (flag[4 * gi + 3] >> 3));
+    // The fourth word's code is 7 where all three carried bits are set.
+    flag[4 * gi + 3] = w0 & w1 & w2 & 0x88888888u;
+  }
+  // Escapes of this owner: population counts go to their own unit, the adds to
+  // the multiply pipe.
+  uint32_t count = (uint32_t)__popc(flag[0]);
+#pragma unroll
+  for (int st = 1; st < 8; ++st) count = mad_lo((uint32_t)__popc(flag[st]), k.one, count);
+  // Inclusive warp scan; shfl.up reports whether the source lane exists.
+  uint32_t inclusive = count;
+#pragma unroll
+  for (int d = 1; d < 32; d <<= 1) {
+    asm("{\n\t.reg .pred p;\n\t.reg .b32 t;\n\t"
+        "shfl.sync.up.b32 t|p, %0, %1, 0, 0xffffffff;\n\t"
+        "@p mad.lo.u32 %0, t, %2, %0;\n\t}"
+        : "+r"(inclusive)
+        : "r"(d), "r"(k.one));
   }
   // A thread consumes at most 64 escapes: clamping its first ordinal bounds
   // every window read below.
-  const int ordinal = min(first_esc + warp_exclusive_sum(count, lane), kEscOrdinalCap - 64);
+  const int ordinal = min(first_esc + (int)(inclusive - count), kEscOrdinalCap - 64);
   __syncwarp();  // expansion and patches visible to the whole warp
 
   uint32_t window = smem_addr(mine) + 4u * (uint32_t)ordinal;
@@ -255,21 +300,41 @@ __device__ __forceinline__ void coded_record_words(const uint8_t* rec, int vlen,
 #pragma unroll
   for (int st = 0; st < 8; ++st) {
     const uint32_t s = sel[st], f = flag[st];
+    const uint32_t s_hi = shift_right_16(s, k);
     uint32_t ha = prmt(tab.p0, tab.p1, s);
-    uint32_t hb = prmt(tab.p0, tab.p1, s >> 16);
+    uint32_t hb = prmt(tab.p0, tab.p1, s_hi);
     // The next eight escape bytes are windows x and x + 4; the second one is
     // only fetched by the (rare) owners with more than four escapes in this word.
     const uint32_t n_here = (uint32_t)__popc(f);
     uint32_t e0, e1 = 0;
     asm("ld.shared.u32 %0, [%1];" : "=r"(e0) : "r"(window) : "memory");
+#ifdef FPB_E1_ALWAYS
+    asm("ld.shared.u32 %0, [%1+16];" : "=r"(e1) : "r"(window) : "memory");
+#elif defined(FPB_E1_BRANCH)
     if (n_here > 4) asm("ld.shared.u32 %0, [%1+16];" : "=r"(e1) : "r"(window) : "memory");
+#else
+    // Predicated inside the statement: an `if` around it becomes a divergent
+    // branch with its convergence bookkeeping, eight times per record.
+    asm("{\n\t.reg .pred p;\n\tsetp.gt.u32 p, %2, 4;\n\t@p ld.shared.u32 %0, [%1+16];\n\t}"
+        : "+r"(e1)
+        : "r"(window), "r"(n_here)
+        : "memory");
+#endif
     window = mad_lo(n_here, k.four, window);
-    // Nibble n of `rank` = escapes among the nibbles below n.
+    // Nibble n of `rank` = escapes among the nibbles below n: the selector that
+    // brings every position the escape byte it would take.
     const uint32_t rank = f * 0x02222222u;
+#ifdef FPB_PICK_MERGE
     // Selector nibble n: n keeps the table byte, 4 + n takes the escape byte.
     const uint32_t pick = (f >> 1) + 0x32103210u;
     ha = prmt(ha, prmt(e0, e1, rank), pick);
-    hb = prmt(hb, prmt(e0, e1, rank >> 16), pick >> 16);
+    hb = prmt(hb, prmt(e0, e1, shift_right_16(rank, k)), pick >> 16);
+#else
+    // Byte masks of the escape positions (code 7 selects the 0xff byte); the
+    // table gave those positions 0x00, so the escape bytes are OR-ed in.
+    ha |= prmt(e0, e1, rank) & prmt(0u, 0xff000000u, s);
+    hb |= prmt(e0, e1, shift_right_16(rank, k)) & prmt(0u, 0xff000000u, s_hi);
+#endif
     // Low bytes are fetched as they are needed (two words per 16-byte chunk):
     // holding all sixteen registers across the loop cost more in lost
     // instruction-level parallelism than the later release of the record costs.

@@ -58,28 +58,46 @@ __device__ __forceinline__ void grid_dependency_wait() {
 
 constexpr long long kWaitCycles = 4000000000LL;  // about two seconds
 
-// Waits for `parity` of `bar` to complete, at most kWaitCycles.  Returns false
-// (and raises the CTA's abort flag) when the wait ran out or the CTA had
+// What a bounded wait needs besides the barrier, kept in the CTA's shared
+// memory so that the fast path of a wait carries no extra registers: the abort
+// flag, the status word to report into and the cycle budget (kWaitCycles in
+// production; tests shorten it to make a wait run out on purpose).
+struct WaitState {
+  int abort;
+  int32_t* status;
+  long long limit;
+};
+
+// Waits for `parity` of `bar` to complete, at most ws->limit cycles.  Returns
+// false (and raises the CTA's abort flag) when the wait ran out or the CTA had
 // already given up.
-static __device__ __noinline__ bool wait_slow(uint64_t* bar, uint32_t parity, volatile int* abort,
-                                       int32_t* status) {
+static __device__ __noinline__ bool wait_slow(uint64_t* bar, uint32_t parity, WaitState* ws) {
+  volatile int* abort = &ws->abort;
   const long long t0 = clock64();
   for (;;) {
+    if (*abort) return false;
 #pragma unroll 1
     for (int i = 0; i < 16; ++i)
       if (mbar_try(bar, parity, 20000u)) return true;
-    if (*abort) return false;
-    if (clock64() - t0 > kWaitCycles) {
+    if (clock64() - t0 > ws->limit) {
       *abort = 1;
-      atomicOr(status, FP_DECODE_WAIT_TIMEOUT);
+      atomicOr(ws->status, FP_DECODE_WAIT_TIMEOUT);
       return false;
     }
   }
 }
-__device__ __forceinline__ bool bounded_wait(uint64_t* bar, uint32_t parity, volatile int* abort,
-                                             int32_t* status) {
+__device__ __forceinline__ bool bounded_wait(uint64_t* bar, uint32_t parity, WaitState* ws) {
   if (mbar_try(bar, parity, 2000u)) return true;
-  return wait_slow(bar, parity, abort, status);
+  return wait_slow(bar, parity, ws);
 }
+
+// Test hook (host side): cycle budget of the bounded waits and the ordinal of
+// one record per CTA that the producer warp leaves out, so that a consumer wait
+// runs out.  Defaults: kWaitCycles, -1 (none).  Set by fp_debug_wait_limit.
+struct WaitDebug {
+  long long limit;
+  long long skip_record;
+};
+WaitDebug wait_debug();
 
 }  // namespace fpb
