@@ -1,13 +1,14 @@
-// HBM KV store kernels for sm_100a: step bookkeeping (prepare / commit), the
-// token writer, the block encoder, the prefill decompressor, and the batch
-// codec entry points.  Behaviour follows fragpack/ops/hbm_kv.cu of the
-// reference (cited per kernel); the byte format is attn_page.py's.
+// HBM KV store kernels for sm_100a: the token writer, the block encoder, the
+// prefill decompressor and the batch codec entry points (the step lifecycle
+// lives in lifecycle.cu).  What they compute follows fragpack/ops/hbm_kv.cu of
+// the reference (cited per kernel); the byte format is attn_page.py's.
 #include <stdarg.h>
 #include <stdio.h>
 
 #include "fp_api.h"
 #include "fp_common.cuh"
 #include "fp_pipe.cuh"
+#include "fp_store.cuh"
 
 namespace fpb {
 
@@ -31,186 +32,16 @@ int cuda_status(cudaError_t err, const char* what) {
 const char* last_error() { return g_error; }
 
 namespace {
+std::atomic<long long> g_wait_limit{kWaitCycles};
+std::atomic<long long> g_skip_record{-1};
+}  // namespace
 
-enum : int { kTagLive = 0, kTagClose = 1, kTagClaim = 2, kTagCloseOnce = 3 };
-constexpr int kPrepareThreads = 1024;
-
-// Device view of fp_store with the address arithmetic of the staging pools.
-struct StoreView {
-  fp_store s;
-  // Staging record `rec` (= kv * H + head) of staging slot `slot` at `layer`.
-  // Slots below S_p are persistent (one record set per layer); the others are
-  // transient scratch that holds a single layer (hbm_kv.cu:80-84).
-  __device__ __forceinline__ uint8_t* staging(int slot, int layer, int rec) const {
-    const int per = 2 * s.H;
-    if (slot < s.S_p) return s.staging + (((int64_t)slot * s.L + layer) * per + rec) * kRawRecord;
-    return s.scratch + ((int64_t)(slot - s.S_p) * per + rec) * kRawRecord;
-  }
-  __device__ __forceinline__ int64_t table_index(int layer, int block, int rec) const {
-    return ((int64_t)layer * s.NB + block) * 2 * s.H + rec;
-  }
-  // Overflow slots are a bitmap so that encodes and imports on different
-  // streams can allocate concurrently (hbm_kv.cu:86-108).
-  __device__ int overflow_take(uint32_t hint) const {
-    for (int i = 0; i < s.ovf_words; ++i) {
-      const int w = (int)((hint + (uint32_t)i) % (uint32_t)s.ovf_words);
-      uint32_t seen = *reinterpret_cast<volatile uint32_t*>(&s.ovf_bits[w]);
-      while (seen != 0xffffffffu) {
-        const uint32_t bit = 1u << (__ffs(~seen) - 1);
-        const uint32_t before = atomicOr(&s.ovf_bits[w], bit);
-        if (!(before & bit)) return 32 * w + (__ffs(bit) - 1);
-        seen = before | bit;
-      }
-    }
-    return -1;
-  }
-  __device__ __forceinline__ void overflow_give_back(int64_t addr) const {
-    const int64_t base = reinterpret_cast<int64_t>(s.overflow);
-    if (addr < base || addr >= base + s.overflow_records * kRawRecord) return;
-    const int slot = (int)((addr - base) / kRawRecord);
-    atomicAnd(&s.ovf_bits[slot >> 5], ~(1u << (slot & 31)));
-  }
-};
-
-// ---------------------------------------------------------------------------
-// prepare: one CTA.  hbm_kv.cu:110-219 of the reference.
-//   1. blocks not listed live lose their persistent staging slot;
-//   2. blocks receiving offset 127 this step are stamped as closing;
-//   3. blocks receiving offset 0 claim staging: their own slot if they kept
-//      one, a transient slot if they also close this step, else a persistent
-//      slot; with none free the block becomes an heir (transient now, the
-//      slot of a block closing this step at commit);
-//   4. closing blocks that own a slot are listed, each persistent one paired
-//      with a waiting heir;
-//   5. every record of a claimed block points at its staging, overflow slots
-//      it held are returned and its arena page is emptied.
-// ---------------------------------------------------------------------------
-__global__ void __launch_bounds__(kPrepareThreads)
-prepare_kernel(StoreView v, const int64_t* slots, int n_tok, const int32_t* live, int n_live,
-               int32_t step) {
-  const fp_store& s = v.s;
-  const int tid = threadIdx.x;
-  int32_t* tag_live = s.tags + kTagLive * s.NB;
-  int32_t* tag_close = s.tags + kTagClose * s.NB;
-  int32_t* tag_claim = s.tags + kTagClaim * s.NB;
-  int32_t* tag_once = s.tags + kTagCloseOnce * s.NB;
-  if (tid == 0) {
-    s.counters[FP_CTR_TRANSIENT] = 0;
-    s.counters[FP_CTR_CLAIMS] = 0;
-    s.counters[FP_CTR_CLOSES] = 0;
-    s.counters[FP_CTR_HEIRS] = 0;
-    s.counters[FP_CTR_DONORS] = 0;
-  }
-  for (int i = tid; i < n_live; i += kPrepareThreads) {
-    const int b = live[i];
-    if (b >= 0 && b < s.NB) tag_live[b] = step;
-  }
-  __syncthreads();
-
-  for (int b = tid; b < s.NB; b += kPrepareThreads) {
-    const int w = s.wslot[b];
-    if (w < 0) continue;
-    if (w >= s.S_p) {
-      s.wslot[b] = -1;  // transient slots never outlive their step
-    } else if (tag_live[b] != step) {
-      s.wslot[b] = -1;
-      s.free_stack[atomicAdd(&s.counters[FP_CTR_FREE_TOP], 1)] = w;
-    }
-  }
-  for (int i = tid; i < n_tok; i += kPrepareThreads) {
-    const int64_t slot = slots[i];
-    if (slot >= 0 && (slot & 127) == 127) tag_close[slot >> 7] = step;
-  }
-  __syncthreads();
-
-  for (int i = tid; i < n_tok; i += kPrepareThreads) {
-    const int64_t slot = slots[i];
-    if (slot < 0 || (slot & 127) != 0) continue;
-    const int b = (int)(slot >> 7);
-    if (atomicExch(&tag_claim[b], step) == step) continue;  // first token only
-    int w = s.wslot[b];
-    if (w < 0) {
-      const bool closes_now = tag_close[b] == step;
-      if (closes_now) {
-        const int t = atomicAdd(&s.counters[FP_CTR_TRANSIENT], 1);
-        if (t < s.S_t) w = s.S_p + t;
-      }
-      if (w < 0) {
-        const int top = atomicSub(&s.counters[FP_CTR_FREE_TOP], 1) - 1;
-        if (top >= 0) {
-          w = s.free_stack[top];
-        } else {
-          atomicAdd(&s.counters[FP_CTR_FREE_TOP], 1);
-          // No persistent slot: wait in transient scratch for a donor.
-          const int t = closes_now ? s.S_t : atomicAdd(&s.counters[FP_CTR_TRANSIENT], 1);
-          if (t < s.S_t) {
-            w = s.S_p + t;
-            s.claim_list[s.cap + atomicAdd(&s.counters[FP_CTR_HEIRS], 1)] = b;
-          } else {
-            atomicAdd(&s.counters[FP_CTR_ERR_STAGING], 1);
-          }
-        }
-      }
-    }
-    s.wslot[b] = w;
-    if (w >= 0) s.claim_list[atomicAdd(&s.counters[FP_CTR_CLAIMS], 1)] = b;
-  }
-  __syncthreads();
-
-  const int heirs = s.counters[FP_CTR_HEIRS];
-  for (int i = tid; i < n_tok; i += kPrepareThreads) {
-    const int64_t slot = slots[i];
-    if (slot < 0 || (slot & 127) != 127) continue;
-    const int b = (int)(slot >> 7);
-    if (atomicExch(&tag_once[b], step) == step) continue;
-    const int w = s.wslot[b];
-    if (w < 0) continue;
-    const int at = atomicAdd(&s.counters[FP_CTR_CLOSES], 1);
-    s.close_list[at] = b;
-    int heir = -1;
-    if (w < s.S_p && heirs > 0) {
-      const int d = atomicAdd(&s.counters[FP_CTR_DONORS], 1);
-      if (d < heirs) heir = s.claim_list[s.cap + d];
-    }
-    s.close_list[s.cap + at] = heir;
-  }
-  __syncthreads();
-  // An heir left without a donor would lose its KV at commit.
-  if (tid == 0 && s.counters[FP_CTR_DONORS] < heirs)
-    atomicAdd(&s.counters[FP_CTR_ERR_STAGING], heirs - s.counters[FP_CTR_DONORS]);
-
-  const int claims = s.counters[FP_CTR_CLAIMS];
-  const int per_block = s.L * 2 * s.H;
-  for (int x = tid; x < claims * per_block; x += kPrepareThreads) {
-    const int b = s.claim_list[x / per_block];
-    const int within = x % per_block, layer = within / (2 * s.H), rec = within % (2 * s.H);
-    const int64_t idx = v.table_index(layer, b, rec);
-    v.overflow_give_back(s.rec_addr[idx]);
-    s.rec_addr[idx] = reinterpret_cast<int64_t>(v.staging(s.wslot[b], layer, rec));
-    s.rec_len[idx] = kRawVarLen;
-    if (rec == 0) s.fill[(int64_t)layer * s.NB + b] = 0;
-  }
+WaitDebug wait_debug() {
+  return WaitDebug{g_wait_limit.load(std::memory_order_relaxed),
+                   g_skip_record.load(std::memory_order_relaxed)};
 }
 
-// commit: hbm_kv.cu:431-448.  Closed blocks free their slot or pass it on.
-__global__ void commit_kernel(StoreView v) {
-  const fp_store& s = v.s;
-  const int closes = s.counters[FP_CTR_CLOSES];
-  for (int i = threadIdx.x; i < closes; i += blockDim.x) {
-    const int b = s.close_list[i];
-    const int w = s.wslot[b];
-    const int heir = s.close_list[s.cap + i];
-    if (heir >= 0) {
-      s.wslot[heir] = w;
-    } else if (w >= 0 && w < s.S_p) {
-      s.free_stack[atomicAdd(&s.counters[FP_CTR_FREE_TOP], 1)] = w;
-    }
-    s.wslot[b] = -1;
-  }
-  __syncthreads();
-  // An emptied close list makes a forward without a fresh prepare encode nothing.
-  if (threadIdx.x == 0) s.counters[FP_CTR_CLOSES] = 0;
-}
+namespace {
 
 // ---------------------------------------------------------------------------
 // Token writer (replaces write_kernel, hbm_kv.cu:221-255): scatters tokens'
@@ -231,35 +62,40 @@ __global__ void commit_kernel(StoreView v) {
 constexpr int kWriteHeads = 4;          // KV heads per CTA
 constexpr int kWriteRow = 272;          // bytes per staged token row (256 + pad)
 
-// One token's K and V rows of `head`, scattered (the general path).
-__device__ __forceinline__ void write_token_scatter(const StoreView& v, const uint16_t* key,
-                                                    const uint16_t* value, int64_t ks0,
-                                                    int64_t ks1, int64_t vs0, int64_t vs1,
-                                                    int64_t token, int w, int off, int layer,
-                                                    int head, int pair) {
-  const fp_store& s = v.s;
-  // K: the token is a row of the A fragment; V: it is a column.
-  const int k_warp = off >> 4, k_j = (off >> 3) & 1, k_g = off & 7;
-  const int v_st = off >> 4, v_f = (off >> 3) & 1, v_c = (off >> 1) & 3, v_e = off & 1;
+// The general path: one token's K and V rows of one head go to their places in
+// the record, one warp per (token, head), lane l carrying dims 4 l .. 4 l + 3
+// (one 8-byte load of each row).  A K token is a row of the A fragment: its
+// dims are spread over all eight word planes, two neighbouring owners per
+// lane, as 4-byte pairs.  A V token is a column: every dim lands in another
+// owner's word as a single scalar.
+__device__ __forceinline__ void scatter_token_row(uint8_t* k_rec, uint8_t* v_rec,
+                                                  const uint16_t* k_row, const uint16_t* v_row,
+                                                  int off, int lane) {
+  // Rows are only known to be 4-byte aligned: two 4-byte loads each.
+  const uint32_t* k32 = reinterpret_cast<const uint32_t*>(k_row) + 2 * lane;
+  const uint32_t* v32 = reinterpret_cast<const uint32_t*>(v_row) + 2 * lane;
+  const uint2 kk = make_uint2(k32[0], k32[1]), vv = make_uint2(v32[0], v32[1]);
   {
-    const uint32_t val =
-        *reinterpret_cast<const uint32_t*>(key + token * ks0 + head * ks1 + 2 * pair);
-    const int st = pair >> 3, f = (pair >> 2) & 1, c = pair & 3;
-    const int owner = 32 * k_warp + 4 * k_g + c;
-    uint8_t* rec = v.staging(w, layer, head);
-    *reinterpret_cast<uint32_t*>(rec + 16 * (kOwners * st + owner) + 4 * (2 * k_j + f)) = val;
+    // dims 4 l .. 4 l + 3 = pairs 2 l and 2 l + 1 of word st = l / 4; inside the
+    // word they are owner columns c = 2 (l & 1) and + 1 of half f = (l / 2) & 1.
+    const int st = lane >> 2, f = (lane >> 1) & 1, c = 2 * (lane & 1);
+    const int owner = 32 * (off >> 4) + 4 * (off & 7) + c;
+    uint8_t* at = k_rec + 16 * (kOwners * st + owner) + 4 * (2 * ((off >> 3) & 1) + f);
+    *reinterpret_cast<uint32_t*>(at) = kk.x;
+    *reinterpret_cast<uint32_t*>(at + 16) = kk.y;
   }
   {
-    const uint32_t val =
-        *reinterpret_cast<const uint32_t*>(value + token * vs0 + head * vs1 + 2 * pair);
-    uint8_t* rec = v.staging(w, layer, s.H + head);
+    // Token `off` is scalar e = off & 1 of pair c = (off / 2) & 3, half
+    // f = (off / 8) & 1 of word st = off / 16, in the owners of its dims.
+    const int st = off >> 4, within = 2 * ((off >> 3) & 1) + (off & 1), c = (off >> 1) & 3;
+    const uint32_t vals[4] = {vv.x & 0xffffu, vv.x >> 16, vv.y & 0xffffu, vv.y >> 16};
 #pragma unroll
-    for (int q = 0; q < 2; ++q) {
-      const int d = 2 * pair + q;
-      const int owner = 32 * (d >> 4) + 4 * (d & 7) + v_c;
-      *reinterpret_cast<uint16_t*>(rec + 16 * (kOwners * v_st + owner) +
-                                   2 * (4 * ((d >> 3) & 1) + 2 * v_f + v_e)) =
-          (uint16_t)(val >> (16 * q));
+    for (int x = 0; x < 4; ++x) {
+      const int d = 4 * lane + x;
+      const int owner = 32 * (d >> 4) + 4 * (d & 7) + c;
+      // j = (d / 8) & 1 selects the register pair of the owner's word.
+      uint8_t* at = v_rec + 16 * (kOwners * st + owner) + 2 * (4 * ((d >> 3) & 1) + within);
+      *reinterpret_cast<uint16_t*>(at) = (uint16_t)vals[x];
     }
   }
 }
@@ -302,12 +138,13 @@ write_kernel(StoreView v, const uint16_t* key, const uint16_t* value, int64_t ks
   }
   __syncthreads();
 
-  // Tokens outside every complete group.
-  for (int k = 0; k < 16; ++k) {
+  // Tokens outside every complete group: one warp per (token, head).
+  for (int x = tid >> 5; x < 16 * heads; x += 8) {
+    const int k = x / heads, head = head0 + x % heads;
     if (tok_slot[k] < 0 || (tok_flags[k] & 1)) continue;
-    for (int x = tid; x < heads * 64; x += 256)
-      write_token_scatter(v, key, value, ks0, ks1, vs0, vs1, t0 + k, tok_slot[k], tok_off[k],
-                          layer, head0 + (x >> 6), x & 63);
+    scatter_token_row(v.staging(tok_slot[k], layer, head), v.staging(tok_slot[k], layer, s.H + head),
+                      key + (t0 + k) * ks0 + head * ks1, value + (t0 + k) * vs0 + head * vs1,
+                      tok_off[k], tid & 31);
   }
 
   // Complete groups that start here (their later tokens may belong to the next CTA's sixteen).
@@ -420,9 +257,10 @@ __device__ __forceinline__ uint2 classes4(const EncodeShared& sh, uint32_t hi) {
   return make_uint2(c0.x | c1.x | c2.x | c3.x, c0.y | c1.y | c2.y | c3.y);
 }
 
-// `place(plan, raw)` runs on thread 0 only and returns where the record goes;
-// it sets `raw` when the record must be stored raw (it does not code, or it
-// codes but no longer fits its page); a null destination drops the record.
+// `place(plan, raw)` is called by all lanes of warp 0 together and returns, in
+// every lane, where the record goes; it sets `raw` when the record must be
+// stored raw (it does not code, or it codes but no longer fits its page); a
+// null destination drops the record.
 template <typename Place>
 __device__ __forceinline__ void encode_cta(const uint4 (&wd)[8], EncodeShared& sh, int tid,
                                            Place&& place) {
@@ -509,13 +347,16 @@ __device__ __forceinline__ void encode_cta(const uint4 (&wd)[8], EncodeShared& s
   EncodePlan plan;
   plan.var_len = (raw_offset + 4 * raw_total + 15) & ~15;
   plan.codes = plan.var_len <= kVarCap && raw_worst <= kMaxWarpRaw;
-  // Thread 0 places the record (global atomics, several microseconds) while the
-  // block builds the variable region in shared memory; the destination is only
-  // needed for the final stores.
-  if (tid == 0) {
+  // Warp 0 places the record (global atomics, several microseconds) while the
+  // other warps build the variable region in shared memory; the destination is
+  // only needed for the final stores.
+  if (warp == 0) {
     bool raw = !plan.codes;
-    sh.dst = place(plan, raw);
-    sh.raw = raw;
+    uint8_t* dst = place(plan, raw);
+    if (lane == 0) {
+      sh.dst = dst;
+      sh.raw = raw;
+    }
   }
   uint32_t* var32 = reinterpret_cast<uint32_t*>(sh.var);
   if (!plan.codes) {
@@ -627,52 +468,65 @@ encode_kernel(StoreView v, int layer, uint8_t* arena, int64_t page_bytes, const 
   }
   __syncthreads();
   encode_cta(wd, sh, tid, [&](const EncodePlan& plan, bool& raw) -> uint8_t* {
+    const int lane = tid & 31;
     int at = -1;
-    if (plan.codes) {
-      // Claim page bytes.  Fast path: one fetch-add (the records of a page are
-      // encoded at the same time, and a compare-and-swap loop on one word
-      // serialises them with retries).  If that overshoots the page the add is
-      // undone and a compare-and-swap loop decides, so that a record too large
-      // for what is left does not block the block's smaller records.
-      int32_t* fill = s.fill + (int64_t)layer * s.NB + block;
-      const int need = kDenseBytes + plan.var_len;
-      const int got = atomicAdd(fill, need);
-      if ((int64_t)got + need <= page_bytes) {
-        at = got;
-      } else {
-        atomicSub(fill, need);
-        int seen = *reinterpret_cast<volatile int32_t*>(fill);
-        while ((int64_t)seen + need <= page_bytes) {
-          const int before = atomicCAS(fill, seen, seen + need);
-          if (before == seen) {
-            at = seen;
-            break;
+    if (lane == 0) {
+      if (plan.codes) {
+        // Claim page bytes.  Fast path: one fetch-add (the records of a page are
+        // encoded at the same time, and a compare-and-swap loop on one word
+        // serialises them with retries).  A claim that would overshoot the page
+        // is undone at once, and a compare-and-swap loop then decides, so that a
+        // record too large for what is left does not block the block's smaller
+        // records.  While some sibling's overshoot is still outstanding the
+        // fill word reads above the page size (a record needs between 22,576
+        // and 24,576 bytes, so honest claims never pass the page size): the
+        // loop waits that out, bounded, before it judges, so a record spills
+        // only when the page really has no room for it.
+        int32_t* fill = s.fill + (int64_t)layer * s.NB + block;
+        const int need = kDenseBytes + plan.var_len;
+        const int got = atomicAdd(fill, need);
+        if ((int64_t)got + need <= page_bytes) {
+          at = got;
+        } else {
+          atomicSub(fill, need);
+          for (int tries = 0; tries < 4096; ++tries) {
+            const int seen = *reinterpret_cast<volatile int32_t*>(fill);
+            if (seen > page_bytes) continue;  // an overshoot about to be undone
+            if ((int64_t)seen + need > page_bytes) break;
+            if (atomicCAS(fill, seen, seen + need) == seen) {
+              at = seen;
+              break;
+            }
           }
-          seen = before;
         }
+        if (at < 0) atomicAdd(&s.counters[FP_CTR_SPILLS], 1);
       }
-      if (at < 0) atomicAdd(&s.counters[FP_CTR_SPILLS], 1);
+      // One add per closed block-layer (by its first record) instead of one per
+      // record: tens of thousands of adds to one address serialise in the L2.
+      if (rec == 0) atomicAdd(&s.counters[FP_CTR_ENCODED], 2 * s.H);
     }
-    // One add per closed block-layer (by its first record) instead of one per
-    // record: tens of thousands of adds to one address serialise in the L2.
-    if (rec == 0) atomicAdd(&s.counters[FP_CTR_ENCODED], 2 * s.H);
+    at = __shfl_sync(0xffffffffu, at, 0);
     if (at >= 0) {
       uint8_t* dst = arena + (int64_t)block * page_bytes + at;
-      s.rec_addr[idx] = reinterpret_cast<int64_t>(dst);
-      s.rec_len[idx] = plan.var_len;
+      if (lane == 0) {
+        s.rec_addr[idx] = reinterpret_cast<int64_t>(dst);
+        s.rec_len[idx] = plan.var_len;
+      }
       raw = false;
       return dst;
     }
     raw = true;
-    atomicAdd(&s.counters[FP_CTR_FALLBACKS], 1);
-    const int slot = v.overflow_take((uint32_t)(block * 2 * s.H + rec));
-    if (slot < 0) {
-      atomicAdd(&s.counters[FP_CTR_ERR_OVERFLOW], 1);
-      return nullptr;
+    const int slot = v.overflow_take_warp((uint32_t)(block * 2 * s.H + rec));
+    if (lane == 0) {
+      atomicAdd(&s.counters[FP_CTR_FALLBACKS], 1);
+      if (slot < 0) atomicAdd(&s.counters[FP_CTR_ERR_OVERFLOW], 1);
     }
+    if (slot < 0) return nullptr;
     uint8_t* dst = s.overflow + (int64_t)slot * kRawRecord;
-    s.rec_addr[idx] = reinterpret_cast<int64_t>(dst);
-    s.rec_len[idx] = kRawVarLen;
+    if (lane == 0) {
+      s.rec_addr[idx] = reinterpret_cast<int64_t>(dst);
+      s.rec_len[idx] = kRawVarLen;
+    }
     return dst;
   });
 }
@@ -810,7 +664,7 @@ struct GatherSmem {
   int32_t vlen[kGatherSlots];
   __align__(8) uint64_t full[kGatherSlots];
   __align__(8) uint64_t empty[kGatherSlots];
-  int abort;
+  WaitState wait;
 };
 static_assert(sizeof(GatherSmem) <= (228 * 1024) / 2 - 1024, "GatherSmem too large for two CTAs per SM");
 
@@ -825,11 +679,15 @@ struct GatherParams {
   int64_t records;  // pages * 2 H
   int H;
   PipeConsts k;
+  int32_t* status;        // g_gather_status on this device
+  long long wait_limit;   // cycle budget of every bounded wait
+  long long skip_record;  // test hook: ordinal of a record the producer leaves out (-1: none)
 };
 
 __device__ __forceinline__ void gather_produce(const GatherParams& p, GatherSmem& sm) {
   const int lane = threadIdx.x & 31;
-  volatile int* abort = &sm.abort;
+  WaitState* const wait = &sm.wait;
+  volatile int* abort = &sm.wait.abort;
   const int per = 2 * p.H;
   uint32_t n = 0;  // records issued so far
   for (int64_t base = blockIdx.x; base < p.records; base += 32LL * gridDim.x) {
@@ -853,8 +711,8 @@ __device__ __forceinline__ void gather_produce(const GatherParams& p, GatherSmem
       const uint32_t slot = n % kGatherSlots, use = n / kGatherSlots;
       if (lane == 0) {
         bool ok = true;
-        if (use > 0) ok = bounded_wait(&sm.empty[slot], (use - 1) & 1, abort, &g_gather_status);
-        if (ok) {
+        if (use > 0) ok = bounded_wait(&sm.empty[slot], (use - 1) & 1, wait);
+        if (ok && (long long)n != p.skip_record) {
           sm.addr[slot] = a;
           sm.vlen[slot] = v;
           sm.tabs[slot] = load_tables(p.plut, p.slut, t);
@@ -877,7 +735,7 @@ __device__ __forceinline__ void gather_produce(const GatherParams& p, GatherSmem
 
 __device__ __forceinline__ void gather_consume(const GatherParams& p, GatherSmem& sm) {
   const int tid = threadIdx.x, lane = tid & 31;
-  volatile int* abort = &sm.abort;
+  WaitState* const wait = &sm.wait;
   const int per = 2 * p.H;
   const OwnerCoords o(tid);
   uint32_t n = 0;
@@ -886,14 +744,17 @@ __device__ __forceinline__ void gather_consume(const GatherParams& p, GatherSmem
     const int rec = (int)(r - page * per);
     const int kv = rec / p.H, head = rec - kv * p.H;
     const uint32_t slot = n % kGatherSlots;
-    bounded_wait(&sm.full[slot], (n / kGatherSlots) & 1, abort, &g_gather_status);
+    // A record whose wait ran out is not decoded (its page keeps what the tile
+    // held; the status word marks the call invalid).
+    const bool landed = bounded_wait(&sm.full[slot], (n / kGatherSlots) & 1, wait);
     const int32_t vlen = sm.vlen[slot];
     auto emit = [&](int st, const uint32_t (&w)[4]) { word_to_tile(sm.tile, kv, o, st, w); };
     auto release = [&] {
       __syncwarp();
       if (lane == 0) mbar_arrive(&sm.empty[slot]);
     };
-    if (vlen > kVarCap || vlen < kHeaderBytes) {
+    if (!landed) {
+    } else if (vlen > kVarCap || vlen < kHeaderBytes) {
       const uint8_t* src = reinterpret_cast<const uint8_t*>(sm.addr[slot]);
       release();
       raw_record_words(src, tid, emit);
@@ -916,7 +777,9 @@ __global__ void __launch_bounds__(kGatherThreads, 2) gather_kernel(GatherParams 
       mbar_init(&sm.full[s], 1);
       mbar_init(&sm.empty[s], kOwners / 32);
     }
-    sm.abort = 0;
+    sm.wait.abort = 0;
+    sm.wait.status = p.status;
+    sm.wait.limit = p.wait_limit;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   __syncthreads();
@@ -928,7 +791,7 @@ __global__ void __launch_bounds__(kGatherThreads, 2) gather_kernel(GatherParams 
   // Nothing may still be writing this CTA's shared memory when it exits (see
   // decode_attn_kernel): after a timeout give copies in flight time to land.
   __syncthreads();
-  if (sm.abort && threadIdx.x == 0) {
+  if (sm.wait.abort && threadIdx.x == 0) {
     const long long t0 = clock64();
     while (clock64() - t0 < 20000000LL) {
     }
@@ -947,22 +810,6 @@ decode_records_kernel(const uint8_t* recs, int64_t rec_stride, const int32_t* re
                  out + i * kRawRecord, 256, threadIdx.x, k);
 }
 
-int check_store(const fp_store* st) {
-  FP_REQUIRE(st != nullptr, "store is null");
-  FP_REQUIRE(st->counters && st->wslot && st->tags && st->free_stack && st->ovf_bits &&
-                 st->claim_list && st->close_list && st->rec_addr && st->rec_len && st->fill,
-             "store has a null table");
-  FP_REQUIRE(st->L > 0 && st->H > 0 && st->NB > 0 && st->cap >= 0, "bad store geometry");
-  return FP_OK;
-}
-
-template <typename Kernel>
-int allow_smem(Kernel kernel, int bytes) {
-  return cuda_status(
-      cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes),
-      "cudaFuncSetAttribute");
-}
-
 }  // namespace
 }  // namespace fpb
 
@@ -973,20 +820,6 @@ extern "C" {
 const char* fp_last_error(void) { return last_error(); }
 
 const char* fp_version(void) { return "fragpack_b200 0.1.0 (sm_100a)"; }
-
-int fp_hbm_prepare(const fp_store* store, const int64_t* slot_mapping, int64_t num_tokens,
-                   const int32_t* live, int64_t num_live, int32_t step, void* stream) {
-  if (int rc = check_store(store)) return rc;
-  FP_REQUIRE(num_tokens >= 0 && num_tokens <= store->cap, "block lists too small for %lld tokens",
-             (long long)num_tokens);
-  FP_REQUIRE(num_tokens == 0 || slot_mapping, "slot_mapping is null");
-  FP_REQUIRE(num_live >= 0 && (num_live == 0 || live), "live list is null");
-  StoreView v{*store};
-  prepare_kernel<<<1, kPrepareThreads, 0, (cudaStream_t)stream>>>(
-      v, slot_mapping, (int)num_tokens, live, (int)num_live, step);
-  FP_LAUNCH_CHECK("prepare_kernel");
-  return FP_OK;
-}
 
 int fp_hbm_write(const fp_store* store, const void* key, int64_t k_stride0, int64_t k_stride1,
                  const void* value, int64_t v_stride0, int64_t v_stride1,
@@ -1030,14 +863,6 @@ int fp_hbm_encode(const fp_store* store, const uint8_t* rank_of, int32_t layer, 
   return FP_OK;
 }
 
-int fp_hbm_commit(const fp_store* store, void* stream) {
-  if (int rc = check_store(store)) return rc;
-  StoreView v{*store};
-  commit_kernel<<<1, 256, 0, (cudaStream_t)stream>>>(v);
-  FP_LAUNCH_CHECK("commit_kernel");
-  return FP_OK;
-}
-
 int fp_hbm_gather(const int32_t* blocks, int64_t n, const int64_t* rec_addr,
                   const int32_t* rec_len, const int32_t* plut, const uint8_t* slut, void* wk,
                   void* wv, int64_t workspace_bytes, int32_t kv_heads, void* stream) {
@@ -1048,8 +873,8 @@ int fp_hbm_gather(const int32_t* blocks, int64_t n, const int64_t* rec_addr,
   FP_REQUIRE(workspace_bytes >= n * 128 * (int64_t)kv_heads * 256, "workspace too small");
   FP_REQUIRE((reinterpret_cast<uintptr_t>(wk) | reinterpret_cast<uintptr_t>(wv)) % 16 == 0,
              "workspace must be 16-byte aligned");
-  static int allowed = allow_smem(gather_kernel, (int)sizeof(GatherSmem));
-  if (allowed) return allowed;
+  static std::atomic<uint64_t> smem_allowed;
+  if (int rc = allow_dynamic_smem(gather_kernel, (int)sizeof(GatherSmem), smem_allowed)) return rc;
   GatherParams p;
   p.blocks = blocks;
   p.rec_addr = rec_addr;
@@ -1061,10 +886,14 @@ int fp_hbm_gather(const int32_t* blocks, int64_t n, const int64_t* rec_addr,
   p.records = n * 2 * kv_heads;
   p.H = kv_heads;
   p.k = pipe_consts();
-  int dev = 0, sms = 148;
-  if (cudaGetDevice(&dev) == cudaSuccess)
-    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-  const int64_t resident = 2LL * sms;
+  void* status_word = nullptr;
+  if (int rc = cuda_status(cudaGetSymbolAddress(&status_word, g_gather_status),
+                           "cudaGetSymbolAddress(g_gather_status)"))
+    return rc;
+  p.status = static_cast<int32_t*>(status_word);
+  p.wait_limit = wait_debug().limit;
+  p.skip_record = wait_debug().skip_record;
+  const int64_t resident = 2LL * device_sms();
   const unsigned grid = (unsigned)(p.records < resident ? p.records : resident);
   gather_kernel<<<grid, kGatherThreads, sizeof(GatherSmem), (cudaStream_t)stream>>>(p);
   FP_LAUNCH_CHECK("gather_kernel");
@@ -1073,8 +902,20 @@ int fp_hbm_gather(const int32_t* blocks, int64_t n, const int64_t* rec_addr,
 
 int fp_hbm_gather_status(int32_t* status) {
   FP_REQUIRE(status, "null status");
-  return cuda_status(cudaMemcpyFromSymbol(status, g_gather_status, sizeof(int32_t)),
-                     "cudaMemcpyFromSymbol(g_gather_status)");
+  if (int rc = cuda_status(cudaMemcpyFromSymbol(status, g_gather_status, sizeof(int32_t)),
+                           "cudaMemcpyFromSymbol(g_gather_status)"))
+    return rc;
+  // Reading clears: the word reports the calls since the previous read.
+  const int32_t zero = 0;
+  return cuda_status(cudaMemcpyToSymbol(g_gather_status, &zero, sizeof(int32_t)),
+                     "cudaMemcpyToSymbol(g_gather_status)");
+}
+
+int fp_debug_wait_limit(int64_t cycles, int64_t skip_record) {
+  FP_REQUIRE(cycles >= 0, "negative wait limit");
+  g_wait_limit.store(cycles > 0 ? cycles : kWaitCycles, std::memory_order_relaxed);
+  g_skip_record.store(skip_record, std::memory_order_relaxed);
+  return FP_OK;
 }
 
 int fp_encode_records(const void* raw, int64_t n, const uint8_t* rank_of,
@@ -1088,8 +929,8 @@ int fp_encode_records(const void* raw, int64_t n, const uint8_t* rank_of,
   FP_REQUIRE((reinterpret_cast<uintptr_t>(raw) | reinterpret_cast<uintptr_t>(out)) % 16 == 0,
              "buffers must be 16-byte aligned");
   constexpr int smem = kTileBytes + (int)sizeof(EncodeShared);
-  static int allowed = allow_smem(encode_records_kernel, smem);
-  if (allowed) return allowed;
+  static std::atomic<uint64_t> smem_allowed;
+  if (int rc = allow_dynamic_smem(encode_records_kernel, smem, smem_allowed)) return rc;
   encode_records_kernel<<<(unsigned)n, kOwners, smem, (cudaStream_t)stream>>>(
       static_cast<const uint8_t*>(raw), rank_of, table_index, kv, out, out_stride, out_len);
   FP_LAUNCH_CHECK("encode_records_kernel");
@@ -1106,8 +947,8 @@ int fp_decode_records(const uint8_t* recs, int64_t rec_stride, const int32_t* re
              "bad rec_stride %lld", (long long)rec_stride);
   FP_REQUIRE((reinterpret_cast<uintptr_t>(recs) | reinterpret_cast<uintptr_t>(out)) % 16 == 0,
              "buffers must be 16-byte aligned");
-  static int allowed = allow_smem(decode_records_kernel, kDecodeSmem);
-  if (allowed) return allowed;
+  static std::atomic<uint64_t> smem_allowed;
+  if (int rc = allow_dynamic_smem(decode_records_kernel, kDecodeSmem, smem_allowed)) return rc;
   decode_records_kernel<<<(unsigned)n, kOwners, kDecodeSmem, (cudaStream_t)stream>>>(
       recs, rec_stride, rec_len, plut, slut, table_index, kv, static_cast<uint8_t*>(out),
       pipe_consts());

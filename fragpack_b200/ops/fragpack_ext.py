@@ -42,6 +42,8 @@ class FpStore(ctypes.Structure):
         ("scratch", c_ptr),
         ("overflow", c_ptr),
         ("fill", c_ptr),
+        ("slot_owner", c_ptr),
+        ("seen_list", c_ptr),
         ("overflow_records", c_i64),
         ("L", c_i32),
         ("H", c_i32),
@@ -86,9 +88,11 @@ _SIGNATURES = {
     "fp_hbm_commit": [c_ptr, c_ptr],
     "fp_hbm_gather": [c_ptr, c_i64, c_ptr, c_ptr, c_ptr, c_ptr, c_ptr, c_ptr, c_i64, c_i32, c_ptr],
     "fp_hbm_gather_status": [c_ptr],
-    "fp_hbm_export": [c_ptr, c_i64, c_ptr, c_ptr, c_ptr, c_i64, c_i64, c_ptr, c_i32, c_i32, c_i32,
-                      c_i64, c_ptr],
-    "fp_hbm_import": [c_ptr, c_ptr, c_i64, c_ptr, c_ptr, c_i64, c_ptr, c_ptr, c_ptr, c_i64, c_ptr],
+    "fp_debug_wait_limit": [c_i64, c_i64],
+    "fp_hbm_export": [c_ptr, c_i64, c_ptr, c_ptr, c_ptr, c_i64, c_i64, c_ptr, c_ptr, c_i32, c_i32,
+                      c_i32, c_i64, c_ptr],
+    "fp_hbm_import": [c_ptr, c_ptr, c_i64, c_ptr, c_ptr, c_i64, c_ptr, c_ptr, c_ptr, c_ptr, c_i64,
+                      c_ptr],
     "fp_encode_records": [c_ptr, c_i64, c_ptr, c_ptr, c_ptr, c_ptr, c_i64, c_ptr, c_ptr],
     "fp_decode_records": [c_ptr, c_i64, c_ptr, c_i64, c_ptr, c_ptr, c_ptr, c_ptr, c_ptr, c_ptr],
 }

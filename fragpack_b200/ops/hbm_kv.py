@@ -52,6 +52,7 @@ _ERR_OVERFLOW = 5
 _FALLBACKS = 6
 _ENCODED = 7
 _SPILLS = 8
+_OVF_FREE = 13
 _N_COUNTERS = 16
 _N_TAGS = 4
 _BLOB_FAILURES = {1: "bad header", 2: "bad lengths", 4: "overflow full"}
@@ -172,6 +173,7 @@ class HbmKvStore:
         self.overflow_records = overflow_records
         self.counters = torch.zeros(_N_COUNTERS, **i32)
         self.counters[0] = staging_slots
+        self.counters[_OVF_FREE] = overflow_records
         self.wslot = torch.full((NB,), -1, **i32)
         self.tags = torch.zeros((_N_TAGS, NB), **i32)
         self.free_stack = torch.arange(staging_slots, **i32)
@@ -184,6 +186,10 @@ class HbmKvStore:
         ).to(dev)
         self.claim_list = torch.zeros(2 * max_tokens, **i32)
         self.close_list = torch.zeros(2 * max_tokens, **i32)
+        # Bookkeeping of this library's prepare: who owns each staging slot,
+        # and the blocks seen opening / closing in the current step.
+        self.slot_owner = torch.full((staging_slots + transient,), -1, **i32)
+        self.seen_list = torch.zeros(2 * max_tokens, **i32)
         # A never-claimed block reads as one all-zero raw record.
         self.null_record = torch.zeros(RAW_RECORD, dtype=torch.uint8, device=dev)
         self.rec_addr = torch.full(
@@ -218,6 +224,8 @@ class HbmKvStore:
             scratch=self.scratch.data_ptr(),
             overflow=self.overflow.data_ptr(),
             fill=self.fill.data_ptr(),
+            slot_owner=self.slot_owner.data_ptr(),
+            seen_list=self.seen_list.data_ptr(),
             overflow_records=overflow_records,
             L=L,
             H=H,
@@ -248,6 +256,8 @@ class HbmKvStore:
             self.ovf_bits,
             self.claim_list,
             self.close_list,
+            self.slot_owner,
+            self.seen_list,
             self.null_record,
             self.rec_addr,
             self.rec_len,
@@ -410,11 +420,16 @@ class HbmKvStore:
         if out.dtype != torch.uint8 or not out.is_contiguous():
             raise RuntimeError("export buffer must be contiguous 16-byte aligned uint8")
         lengths = torch.empty(blocks.numel(), dtype=torch.int64, device=out.device)
+        # Offset of every record in its blob, written by the layout pass for the copy pass.
+        scratch = torch.empty(
+            (blocks.numel(), self.num_layers * 2 * self.kv_heads), dtype=torch.int64, device=out.device
+        )
         check(
             extension().fp_hbm_export(
                 blocks.data_ptr(), blocks.numel(), self.rec_addr.data_ptr(),
                 self.rec_len.data_ptr(), out.data_ptr(), out.numel(), stride, lengths.data_ptr(),
-                self.num_layers, self.kv_heads, self.num_blocks, self.table_digest, stream_ptr(),
+                scratch.data_ptr(), self.num_layers, self.kv_heads, self.num_blocks,
+                self.table_digest, stream_ptr(),
             )
         )
         return lengths
@@ -443,10 +458,15 @@ class HbmKvStore:
         ):
             raise RuntimeError("import metadata must be int64 offsets, int32 blocks / status")
         status = torch.zeros(blocks.numel(), dtype=torch.int32, device=src.device)
+        # Source and destination address of every record, from the layout and
+        # placement passes to the copy pass.
+        scratch = torch.empty(
+            (2, blocks.numel(), self.num_layers * 2 * self.kv_heads), dtype=torch.int64, device=src.device
+        )
         check(
             extension().fp_hbm_import(
                 self._store_ref, src.data_ptr(), src.numel(), offsets.data_ptr(),
-                blocks.data_ptr(), blocks.numel(), status.data_ptr(),
+                blocks.data_ptr(), blocks.numel(), status.data_ptr(), scratch.data_ptr(),
                 self.arena_base_dev.data_ptr(), self.arena_stride_dev.data_ptr(),
                 self.table_digest, stream_ptr(),
             )

@@ -43,6 +43,9 @@ enum {
   FP_CTR_SPILLS = 8,
   FP_CTR_HEIRS = 9,
   FP_CTR_DONORS = 10,
+  FP_CTR_SEEN_OPEN = 11,  /* blocks seen opening this step (prepare's scan) */
+  FP_CTR_SEEN_CLOSE = 12, /* blocks seen closing this step */
+  FP_CTR_OVF_FREE = 13,   /* free overflow slots; initialise to overflow_records */
   FP_NUM_COUNTERS = 16
 };
 
@@ -59,7 +62,12 @@ enum { FP_PEER_WAIT_TIMEOUT = 1 };
 
 /*
  * The store state that the reference passes as 13 positional tensors to every
- * hbm_* function (fragpack/ops/hbm_kv.py:287-301, hbm_kv.cu:32-78).
+ * hbm_* function (fragpack/ops/hbm_kv.py:287-301, hbm_kv.cu:32-78), plus the
+ * two tables this library's prepare uses (slot_owner, seen_list).  The caller
+ * allocates everything, zero-filled except: wslot and slot_owner -1,
+ * free_stack 0 .. S_p - 1 with counters[FP_CTR_FREE_TOP] = S_p, the bits of
+ * ovf_bits past the pool set with counters[FP_CTR_OVF_FREE] = overflow_records,
+ * rec_addr pointing at an all-zero raw record with rec_len 10240.
  */
 typedef struct fp_store {
   int32_t* counters;    /* [FP_NUM_COUNTERS] */
@@ -75,6 +83,8 @@ typedef struct fp_store {
   uint8_t* scratch;     /* [S_t, 2, H, 32768] one layer of transient staging */
   uint8_t* overflow;    /* [O, 32768] raw records that do not code or fit */
   int32_t* fill;        /* [L, NB] bytes used in each block-layer page */
+  int32_t* slot_owner;  /* [S_p + S_t] block that owns each staging slot, -1 if free */
+  int32_t* seen_list;   /* [2, cap] blocks seen opening, then closing, this step */
   int64_t overflow_records; /* O */
   int32_t L, H, NB, S_p, S_t, ovf_words, cap;
 } fp_store;
@@ -251,20 +261,48 @@ int fp_hbm_gather(const int32_t* blocks, int64_t n, const int64_t* rec_addr,
                   void* wv, int64_t workspace_bytes, int32_t kv_heads, void* stream);
 
 /* Copies the decompressor's status word to the host (synchronises the device's
- * prior work on the legacy stream); zero in normal operation.  No counterpart
- * in the reference. */
+ * prior work on the legacy stream) and clears it, so that each read reports the
+ * calls since the previous one; zero in normal operation.  No counterpart in
+ * the reference. */
 int fp_hbm_gather_status(int32_t* status);
 
-/* hbm_export (fragpack/ops/hbm_kv.cu:755-774): closed blocks -> block blobs. */
+/*
+ * Test hook, no counterpart in the reference.  Every device-side wait of this
+ * library gives up after a cycle budget (about two seconds) and reports through
+ * a status word instead of hanging.  This call sets that budget for the
+ * launches that follow (`cycles` > 0; 0 restores the default) and names one
+ * record per CTA, by its ordinal in the CTA's stream, that the producer warp
+ * will leave out (`skip_record` >= 0; -1 none), so that a test can make a wait
+ * run out, on purpose and harmlessly, and check the status word.  Process-wide;
+ * not for production use.
+ */
+int fp_debug_wait_limit(int64_t cycles, int64_t skip_record);
+
+/*
+ * hbm_export (fragpack/ops/hbm_kv.cu:755-774): closed blocks -> block blobs.
+ * Blob i is written at out + i * stride and lengths[i] receives its size (a
+ * 4096 multiple).  `scratch` is int64 [n, L * 2 * H] device memory of the
+ * caller: the layout pass leaves every record's offset there for the copy pass
+ * (one CTA per record).  Any number of KV heads.
+ */
 int fp_hbm_export(const int32_t* blocks, int64_t n, const int64_t* rec_addr,
                   const int32_t* rec_len, uint8_t* out, int64_t out_bytes, int64_t stride,
-                  int64_t* lengths, int32_t L, int32_t H, int32_t NB, int64_t digest, void* stream);
+                  int64_t* lengths, int64_t* scratch, int32_t L, int32_t H, int32_t NB,
+                  int64_t digest, void* stream);
 
-/* hbm_import (fragpack/ops/hbm_kv.cu:776-802): block blobs -> blocks of this store. */
+/*
+ * hbm_import (fragpack/ops/hbm_kv.cu:776-802): block blobs -> blocks of this
+ * store.  status[i] (zeroed by the caller) receives FP_BLOB_* bits; a blob with
+ * a bad header or length table is left alone, a layer that finds the overflow
+ * pool full keeps its old records.  `scratch` is int64 [2, n, L * 2 * H] device
+ * memory of the caller (source and destination address of every record).  A
+ * replaced record's overflow slot is returned only after the new record is in
+ * place.  Any number of KV heads.
+ */
 int fp_hbm_import(const fp_store* store, const uint8_t* src, int64_t src_bytes,
                   const int64_t* offsets, const int32_t* blocks, int64_t n, int32_t* status,
-                  const int64_t* arena_base, const int64_t* arena_stride, int64_t digest,
-                  void* stream);
+                  int64_t* scratch, const int64_t* arena_base, const int64_t* arena_stride,
+                  int64_t digest, void* stream);
 
 /*
  * Batch form of attn_page.encode_record (fragpack/compression/attn_page.py:146-209)
