@@ -295,3 +295,15 @@ int fpo_threads(void) {
   return 1;
 #endif
 }
+
+/* Sets the host threads of the batch forms (a launcher may have pinned the
+ * OpenMP default to one); returns what is now in force. */
+int fpo_set_threads(int n) {
+#ifdef _OPENMP
+  if (n > 0) omp_set_num_threads(n);
+  return omp_get_max_threads();
+#else
+  (void)n;
+  return 1;
+#endif
+}

@@ -66,3 +66,21 @@ def gpu_decode(recs: np.ndarray, lens: np.ndarray, tables: np.ndarray, kv: np.nd
     )
     torch.cuda.synchronize()
     return out.cpu().numpy().view(np.uint16)
+
+
+def record_bytes(work, layer: int, block: int, kv: int, head: int) -> bytes:
+    """Bytes of one record of a built workload, wherever the store put it.
+
+    A record lives in its block's arena page, in staging (an open block), in
+    the overflow pool, or is the shared all-zero record of a never-written block.
+    """
+    store = work.store
+    addr = int(store.rec_addr[layer, block, kv, head].item())
+    n = int(store.rec_len[layer, block, kv, head].item()) + ap.DENSE_BYTES
+    pools = [*work.arenas, store.staging, store.scratch, store.overflow, store.null_record]
+    for pool in pools:
+        base = pool.data_ptr()
+        if base <= addr < base + pool.numel() * pool.element_size():
+            flat = pool.view(-1).view(torch.uint8)
+            return flat[addr - base : addr - base + n].cpu().numpy().tobytes()
+    raise AssertionError("record address outside every pool of the store")

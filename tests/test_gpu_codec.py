@@ -12,7 +12,7 @@ import numpy as np
 import pytest
 
 import oracle
-from fragpack_b200 import synth
+from benchmarks import synth
 from fragpack_b200.compression import attn_page as ap
 from tests._util import gpu_decode, gpu_encode
 

@@ -18,7 +18,7 @@ import numpy as np
 import pytest
 import torch
 
-from fragpack_b200 import workloads
+from benchmarks import workloads
 from fragpack_b200.ops.fragpack_ext import FpPeers, check, extension, stream_ptr
 from fragpack_b200.ops.fused_attn_decode import (
     RecordTables,
