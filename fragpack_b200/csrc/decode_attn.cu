@@ -36,16 +36,20 @@ namespace {
 constexpr int kConsumerWarps = 8;
 constexpr int kConsumers = 32 * kConsumerWarps;  // 256 = fragment owners
 constexpr int kThreads = kConsumers + 32;        // + producer warp
-// Resident CTAs per SM the kernels are shaped for.  Two: a three-slot record
-// ring and separate escape scratch for K and V records.  Three (more warps to
-// hide the decode's latencies, 72 registers per thread): a two-slot ring and
-// one escape scratch, which costs a barrier at the end of every page.
-#ifndef FPB_CTAS_PER_SM
-#define FPB_CTAS_PER_SM 2
-#endif
-constexpr int kCtasPerSm = FPB_CTAS_PER_SM;
-constexpr int kSlots = kCtasPerSm == 3 ? 2 : 3;
-constexpr int kEscBuffers = kCtasPerSm == 3 ? 1 : 2;
+// Ring slots of the plain comparison kernel (always two CTAs per SM).
+constexpr int kSlots = 3;
+// The fused kernel comes in two shapes, named by the CTAs that fit one SM.
+// Two: a three-slot record ring, separate escape scratch for K and V records,
+// 96 registers per thread.  Three: half as many warps again to hide the
+// decode's latencies, paid for with a two-slot ring, one escape scratch for K
+// and V (hence a barrier at the end of every page) and 72 registers.  The
+// three-CTA shape wins where CTAs stream many pages each (long contexts, big
+// batches); the two-CTA shape where a CTA sees only a handful of pages.
+template <int kCtas>
+struct Shape {
+  static constexpr int kSlots = kCtas == 3 ? 2 : 3;
+  static constexpr int kEscBuffers = kCtas == 3 ? 1 : 2;
+};
 constexpr int kSlotBytes = kCodedMax;            // raw records are read in place
 constexpr int kPRow = 80;                        // bytes per (head, c) row of P, padded
 constexpr int kPBytes = 32 * kPRow;
@@ -61,10 +65,13 @@ struct SlotDesc {
   int32_t seq_index, first_page, pages, seq_len;
 };
 
+template <int kCtas>
 struct Smem {
+  static constexpr int kSlots = Shape<kCtas>::kSlots;
+  static constexpr int kEscBuffers = Shape<kCtas>::kEscBuffers;
   __align__(128) uint8_t slots[kSlots][kSlotBytes];
-  // K and V records expand their escapes into separate buffers: the V decode of
-  // a page and the K decode of the next one run without a barrier between them.
+  // With two buffers K and V records expand their escapes apart: the V decode
+  // of a page and the K decode of the next one run without a barrier between.
   __align__(16) uint8_t esc[kEscBuffers][kEscBytes];
   __align__(16) uint8_t p[2][kPBytes];
   __align__(16) float ref[2][kConsumerWarps][8];
@@ -79,8 +86,9 @@ struct Smem {
   WaitState wait;
 };
 
-// kCtasPerSm CTAs must fit one SM: 228 KB per SM, 1 KB reserved per CTA.
-static_assert(sizeof(Smem) <= (228 * 1024) / kCtasPerSm - 1024, "Smem too large for the CTAs per SM");
+// kCtas CTAs must fit one SM: 228 KB per SM, 1 KB reserved per CTA.
+static_assert(sizeof(Smem<2>) <= (228 * 1024) / 2 - 1024, "Smem<2> too large for two CTAs per SM");
+static_assert(sizeof(Smem<3>) <= (228 * 1024) / 3 - 1024, "Smem<3> too large for three CTAs per SM");
 
 struct DecodeParams {
   const uint32_t* q;
@@ -179,8 +187,9 @@ __device__ __forceinline__ bool load_item(const DecodeParams& p, int item, Item&
 // kDynamic: items beyond the CTA's first come first come, first served from
 // the launch's counter in the plan (CTAs that share an SM, or that got shorter
 // items, come back sooner) and every record's descriptor names its item.
-template <bool kDynamic>
-__device__ __forceinline__ void produce(const DecodeParams& p, Smem& sm) {
+template <bool kDynamic, int kCtas>
+__device__ __forceinline__ void produce(const DecodeParams& p, Smem<kCtas>& sm) {
+  constexpr int kSlots = Shape<kCtas>::kSlots;
   const int lane = threadIdx.x & 31;
   WaitState* const wait = &sm.wait;
   volatile int* abort = &sm.wait.abort;
@@ -249,17 +258,6 @@ __device__ __forceinline__ void produce(const DecodeParams& p, Smem& sm) {
       for (int j = 0; j < 2 * count; ++j) {
         if (kDynamic && base + 32 >= it.pages && j == 2 * count - 1) upcoming = take();
         const int src = j >> 1;
-#ifdef FPB_L2_AHEAD
-        // The ring holds few records; the lane that resolved a page a little
-        // further on brings its record into the L2 meanwhile, so that the copy
-        // into the slot that frees up next starts from there.
-        if (lane == src + FPB_L2_AHEAD && lane < count) {
-          const int32_t n = (j & 1) ? len_v : len_k;
-          if (n <= kVarCap && n >= kHeaderBytes)
-            prefetch_l2(reinterpret_cast<const void*>((j & 1) ? addr_v : addr_k),
-                        (uint32_t)(kDenseBytes + (n & ~15)));
-        }
-#endif
         const int64_t addr = __shfl_sync(0xffffffffu, (j & 1) ? addr_v : addr_k, src);
         const int32_t vlen = __shfl_sync(0xffffffffu, (j & 1) ? len_v : len_k, src);
         const uint32_t slot = r % kSlots, use = r / kSlots;
@@ -313,8 +311,10 @@ __device__ __forceinline__ void produce(const DecodeParams& p, Smem& sm) {
 // ---------------------------------------------------------------------------
 // Consumer warps
 // ---------------------------------------------------------------------------
-template <bool kDynamic>
-__device__ __forceinline__ void consume(const DecodeParams& p, Smem& sm) {
+template <bool kDynamic, int kCtas>
+__device__ __forceinline__ void consume(const DecodeParams& p, Smem<kCtas>& sm) {
+  constexpr int kSlots = Shape<kCtas>::kSlots;
+  constexpr int kEscBuffers = Shape<kCtas>::kEscBuffers;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int g = lane >> 2, c = lane & 3;
   WaitState* const wait = &sm.wait;
@@ -540,10 +540,11 @@ __device__ __forceinline__ void consume(const DecodeParams& p, Smem& sm) {
   }
 }
 
-template <bool kDynamic>
-__global__ void __launch_bounds__(kThreads, kCtasPerSm) decode_attn_kernel(DecodeParams p) {
+template <bool kDynamic, int kCtas>
+__global__ void __launch_bounds__(kThreads, kCtas) decode_attn_kernel(DecodeParams p) {
+  constexpr int kSlots = Shape<kCtas>::kSlots;
   extern __shared__ __align__(128) uint8_t dyn[];
-  Smem& sm = *reinterpret_cast<Smem*>(dyn);
+  Smem<kCtas>& sm = *reinterpret_cast<Smem<kCtas>*>(dyn);
   if (threadIdx.x == 0) {
     for (int s = 0; s < kSlots; ++s) {
       mbar_init(&sm.full[s], 1);
@@ -562,13 +563,13 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) decode_attn_kernel(Decod
   // arrival has been counted, see produce.)
   if (threadIdx.x >= kConsumers) {
     if (!kDynamic) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-    produce<kDynamic>(p, sm);
+    produce<kDynamic, kCtas>(p, sm);
   } else {
     // With the dynamic schedule the producer warp alone allows dependents,
     // after its arrival has been counted (the instruction takes effect with
     // the first thread of the CTA that issues it).
     if (!kDynamic) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-    consume<kDynamic>(p, sm);
+    consume<kDynamic, kCtas>(p, sm);
   }
   // Nothing may still be writing this CTA's shared memory when it exits: on
   // the normal path every issued copy has been consumed; after a timeout give
@@ -1270,7 +1271,14 @@ int launch_decode(bool plain, const fp_peers* peers, int buffer, const void* q, 
              "out rows must be 4-byte aligned (8-byte in a peer group)");
   FP_REQUIRE(reinterpret_cast<uintptr_t>(out) % 4 == 0, "out rows must be 4-byte aligned");
   const int sms = num_sms > 0 ? num_sms : device_sms();
-  const int slots = (plain ? 2 : kCtasPerSm) * sms;
+  // The fused kernel's shape (see Shape): three CTAs per SM when the CTAs will
+  // stream many pages each.  The rule reads the call's shape only - sequence x
+  // head pairs times the block-table width (an upper bound of the pages of a
+  // sequence), per CTA of the two-CTA grid - so every layer of a step, and
+  // every replay of a captured graph, takes the same kernel.
+  const long long pages_bound = (long long)batch * kv_heads * (bt_stride > 0 ? bt_stride : 1);
+  const bool three = !plain && pages_bound >= 24LL * 2 * sms;
+  const int slots = (three ? 3 : 2) * sms;
   cudaStream_t st = (cudaStream_t)stream;
   // More (sequence, head) pairs than resident CTAs: CTAs run several items, of
   // ragged sizes in a ragged batch, and taking them first come, first served
@@ -1306,12 +1314,15 @@ int launch_decode(bool plain, const fp_peers* peers, int buffer, const void* q, 
   p.skip_record = wait_debug().skip_record;
   void (*kernel)(DecodeParams) =
       plain ? (dynamic ? plain_attn_kernel<true> : plain_attn_kernel<false>)
-            : (dynamic ? decode_attn_kernel<true> : decode_attn_kernel<false>);
+      : three ? (dynamic ? decode_attn_kernel<true, 3> : decode_attn_kernel<false, 3>)
+              : (dynamic ? decode_attn_kernel<true, 2> : decode_attn_kernel<false, 2>);
   const char* name = plain ? "plain_attn_kernel" : "decode_attn_kernel";
-  const int smem = plain ? (int)sizeof(PlainSmem) : (int)sizeof(Smem);
+  const int smem = plain ? (int)sizeof(PlainSmem)
+                         : three ? (int)sizeof(Smem<3>) : (int)sizeof(Smem<2>);
   // The shared memory limit is set once per device and kernel, not per call.
-  static std::atomic<uint64_t> smem_allowed[4];
-  if (int rc = allow_dynamic_smem(kernel, smem, smem_allowed[(plain ? 2 : 0) + (dynamic ? 1 : 0)]))
+  static std::atomic<uint64_t> smem_allowed[6];
+  if (int rc = allow_dynamic_smem(kernel, smem,
+                                  smem_allowed[(plain ? 4 : three ? 2 : 0) + (dynamic ? 1 : 0)]))
     return rc;
   const long long max_items = (long long)units * kv_heads;
   const int grid = (int)(max_items < slots ? max_items : slots);

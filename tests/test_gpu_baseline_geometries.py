@@ -48,6 +48,8 @@ CASES = {
     "c4": dict(base="c4", layers=1, batch=2, ctx_min=1024, ctx_max=1024, junk=0.009),
     # The same at the nominal 2 % junk: every record falls back to raw.
     "c4-junk2": dict(base="c4", layers=1, batch=1, ctx_min=512, ctx_max=512, junk=0.02),
+    # The MHA geometry without junk, for attention (group 1, 32 KV heads).
+    "c4-clean": dict(base="c4", layers=1, batch=2, ctx_min=1024, ctx_max=1024, junk=0.0),
     # Llama-3-70B-like: 8 KV heads, GQA 8, 256 blocks per sequence.
     "c5": dict(base="c5", layers=1, batch=2),
 }
@@ -120,7 +122,7 @@ def test_records_equal_oracle_bytes(case) -> None:
     assert checked > 0
     if name == "c4-junk2":
         assert raw_seen == checked  # 2 % junk: nothing codes
-    if name in ("c2", "c5"):
+    if name in ("c2", "c5", "c4-clean"):
         assert raw_seen == 0
     if not name.startswith("c4"):
         assert spilled == 0
@@ -146,6 +148,11 @@ def test_decompressor_returns_written_bits(case) -> None:
 
 def test_decode_attention_within_the_stated_tolerance(case) -> None:
     name, cfg, work = case
+    if cfg.junk:
+        # Junk scalars are arbitrary finite bit patterns, up to 3e38: their scores
+        # overflow fp32 in any attention, the fp32 reference included.  Configuration
+        # 4 measures the prefill side; its geometry is attended in the junk-free case.
+        pytest.skip("random-bit-pattern KV overflows fp32 attention")
     device = work.block_table.device
     B, H, G = work.cfg.batch, work.cfg.kv_heads, work.cfg.group
     sms = torch.cuda.get_device_properties(device).multi_processor_count

@@ -14,7 +14,7 @@ must give exactly what ``fp_fused_decode`` gives with a caller-owned workspace
 - the same kernels run with the same plan, and the merge order is fixed by the
 plan, so the outputs are equal bit for bit - and, like every decode test, must
 match fp32 attention over the written KV (the oracle) within 1e-2 max-abs and
-2e-3 mean-abs.
+2e-3 mean-abs (relative to the magnitude for outputs above 1).
 """
 
 from __future__ import annotations
@@ -24,6 +24,7 @@ import torch
 
 import oracle
 from benchmarks import workloads
+from tests._util import assert_attention_close
 from fragpack_b200.ops.fragpack_ext import check, extension, stream_ptr
 from fragpack_b200.ops.fused_attn_decode import (
     RecordTables,
@@ -82,8 +83,7 @@ def test_noalloc_matches_workspace_entry_point_twice_in_a_row() -> None:
                 ref = oracle.attention_fp32(
                     q[b, h * G : (h + 1) * G].float().cpu(), kv[0][:n, h], kv[1][:n, h], SCALE
                 )
-                err = (got[b, h * G : (h + 1) * G].float().cpu() - ref).abs()
-                assert err.max().item() <= 1e-2 and err.mean().item() <= 2e-3
+                assert_attention_close(got[b, h * G : (h + 1) * G], ref, (n, b, h))
 
 
 def test_noalloc_rejects_sizes_beyond_its_scratch() -> None:
