@@ -9,10 +9,10 @@ under a gigabyte.  For each:
   (``attn_page.encode_record``; raw tails equal the staging layout);
 * the prefill decompressor returns the written bits;
 * decode attention matches fp32 attention over the written KV within the
-  stated 1e-2 max-abs / 2e-3 mean-abs on BF16 outputs.  Outputs of magnitude
+  stated 1e-2 max-abs / 2e-3 mean-abs on BF16 outputs; outputs of magnitude
   above 1 (the x64 heavy tails of configuration 3 reach ~100, where BF16 is
-  spaced 0.5 apart) are held to the same bounds relative to their magnitude;
-  both forms are asserted, each on its own elements.
+  spaced 0.5 apart) are bounded relative to their magnitude (see
+  ``tests/_util.assert_attention_close``); both forms are asserted.
 """
 
 from __future__ import annotations
@@ -33,7 +33,7 @@ from fragpack_b200.ops.fused_attn_decode import (
     decode_units,
     workspace_elems,
 )
-from tests._util import bits_of, record_bytes
+from tests._util import assert_attention_close, bits_of, record_bytes
 
 pytestmark = pytest.mark.gpu
 SCALE = 128**-0.5
@@ -176,19 +176,10 @@ def test_decode_attention_within_the_stated_tolerance(case) -> None:
         torch.cuda.synchronize()
         assert decode_status(ws, units) == 0
         assert not torch.isnan(out).any()
-        small, large = [], []
         for b in range(min(2, B)):
             kv = work.sample[(layer, b)].float().cpu()
             for h in range(H):
                 ref = oracle.attention_fp32(
                     q[b, h * G : (h + 1) * G].float().cpu(), kv[0][:, h], kv[1][:, h], SCALE
                 )
-                err = (out[b, h * G : (h + 1) * G].float().cpu() - ref).abs()
-                big = ref.abs() > 1.0
-                small.append(err[~big])
-                large.append((err / ref.abs().clamp(min=1.0))[big])
-        small, large = torch.cat(small), torch.cat(large)
-        assert small.numel() > 0
-        assert small.max().item() <= 1e-2 and small.mean().item() <= 2e-3, (name, layer)
-        if large.numel():
-            assert large.max().item() <= 1e-2 and large.mean().item() <= 2e-3, (name, layer)
+                assert_attention_close(out[b, h * G : (h + 1) * G], ref, (name, layer, b, h))
