@@ -13,7 +13,7 @@ import subprocess
 import sys
 
 _DIR = Path(__file__).resolve().parent
-SOURCES = ("hbm_kv.cu", "lifecycle.cu", "decode_attn.cu", "blob.cu")
+SOURCES = ("hbm_kv.cu", "lifecycle.cu", "decode_attn.cu", "blob.cu", "prefill_attn.cu")
 HEADERS = ("fp_common.cuh", "fp_pipe.cuh", "fp_store.cuh", "fp_api.h", "../../include/fragpack_b200.h")
 LIBRARY = _DIR.parent / "ops" / "libfragpack_b200.so"
 NVCC_FLAGS = (

@@ -82,6 +82,8 @@ _SIGNATURES = {
                         c_ptr],
     "fp_fused_decode_noalloc": [c_ptr, c_i64, c_ptr, c_ptr, c_ptr, c_ptr, c_ptr, c_i64, c_ptr, c_ptr,
                                 c_i64, c_i32, c_i32, c_i32, c_i32, c_i32, c_f32, c_i32, c_ptr],
+    "fp_prefill_attention": [c_ptr, c_i64, c_ptr, c_ptr, c_ptr, c_ptr, c_ptr, c_i64, c_ptr, c_ptr, c_ptr,
+                             c_i64, c_i32, c_i32, c_i32, c_i32, c_f32, c_ptr, c_ptr],
     "fp_hbm_prepare": [c_ptr, c_ptr, c_i64, c_ptr, c_i64, c_i32, c_ptr],
     "fp_hbm_write": [c_ptr, c_ptr, c_i64, c_i64, c_ptr, c_i64, c_i64, c_ptr, c_i64, c_i32, c_ptr],
     "fp_hbm_encode": [c_ptr, c_ptr, c_i32, c_ptr, c_i64, c_i64, c_ptr],

@@ -225,6 +225,33 @@ int fp_fused_decode_noalloc(const void* q, int64_t q_stride, const int64_t* rec_
                             int32_t kv_heads, int32_t group, int32_t units, int32_t replan,
                             float scale, int32_t num_sms, void* stream);
 
+/*
+ * Causal prefill attention directly over compressed records.  Replaces the
+ * gather + FlashAttention step of the reference's prefill path
+ * (fragpack/integrations/vllm/backend.py:560-575: store.gather, then
+ * flash_attn_varlen_func over the BF16 workspace) by one kernel that decodes
+ * the records into shared-memory operand tiles and runs both products on the
+ * tensor cores (tcgen05); the decompressed KV is never written to HBM.
+ *
+ *   q, out      BF16 [T, H * group, 128]; row strides in elements (multiples of 8)
+ *   rec_addr/rec_len, plut/slut   one layer, as for fp_fused_decode
+ *   block_table int32 [R, >= pages]; row stride in elements
+ *   q_start     int32 [R + 1]: request r owns query rows q_start[r] .. q_start[r + 1]
+ *   ctx_len     int32 [R]: its context length, the new tokens included (they
+ *               must already be in the store: fp_hbm_write comes first)
+ *   max_query_tokens  the most query rows of any request (sizes the grid)
+ *   status      one int32 of the caller, zeroed once: the kernel ORs
+ *               FP_DECODE_WAIT_TIMEOUT into it when a bounded wait ran out
+ * Query i of request r sits at position ctx_len[r] - n_r + i and attends the
+ * keys up to and including itself.
+ */
+int fp_prefill_attention(const void* q, int64_t q_stride, const int64_t* rec_addr,
+                         const int32_t* rec_len, const int32_t* plut, const uint8_t* slut,
+                         const int32_t* block_table, int64_t bt_stride, const int32_t* q_start,
+                         const int32_t* ctx_len, void* out, int64_t out_stride, int32_t num_requests,
+                         int32_t max_query_tokens, int32_t kv_heads, int32_t group, float scale,
+                         int32_t* status, void* stream);
+
 /* hbm_prepare (fragpack/ops/hbm_kv.cu:669-686): start a step. */
 int fp_hbm_prepare(const fp_store* store, const int64_t* slot_mapping, int64_t num_tokens,
                    const int32_t* live, int64_t num_live, int32_t step, void* stream);
