@@ -916,6 +916,99 @@ def run_codec(args, junk: float, layers: int = 2, steps: int | None = None) -> d
     return out
 
 
+def run_prefill_attention(args, requests: int = 4, cached: int = 2048, chunk: int = 512) -> dict:
+    """Prefill attention of a chunk over cached context, MHA geometry of configuration 4.
+
+    ``requests`` sequences hold ``cached + chunk`` tokens in the store (32 KV
+    heads, group 1, junk-free values: junk bit patterns overflow fp32 attention
+    in any implementation); the last ``chunk`` tokens of each are the queries.
+    Two paths over the same store: the fused kernel (records decoded into
+    tensor-core operand tiles, nothing written back) and the reference's two
+    steps (decompress into the BF16 workspace, then attention over it - torch
+    SDPA per request where the reference calls FlashAttention-3).
+    """
+    from fragpack_b200.integrations.vllm.backend import plan_prefill_groups, workspace_prefill_attention
+    from fragpack_b200.ops.fused_attn_decode import RecordTables
+    from fragpack_b200.ops.prefill_attn import prefill_attention, prefill_status
+
+    device = torch.device("cuda", 0)
+    total = cached + chunk
+    cfg = replace(workloads.CONFIGS["c4"], name="c4-mha-chunked-prefill", batch=requests, ctx_min=total,
+                  ctx_max=total, junk=0.0)
+    work = workloads.build_decode_workload(cfg, device, seed=args.seed, layers=1, keep_layers=(0,), keep_seqs=1)
+    H, G = work.cfg.kv_heads, work.cfg.group
+    gen = torch.Generator(device=device).manual_seed(args.seed + 9)
+    q = torch.randn(requests * chunk, H * G, 128, generator=gen, device=device).to(torch.bfloat16)
+    tabs = RecordTables(*work.store.layer_tables(0))
+    q_start = torch.arange(0, requests * chunk + 1, chunk, dtype=torch.int32, device=device)
+    ctx_lens = torch.full((requests,), total, dtype=torch.int32, device=device)
+    out_fused = torch.full_like(q, float("nan"))
+    out_two = torch.full_like(q, float("nan"))
+    pages = total // 128
+    wk = torch.empty(requests * pages, 128, H, 128, dtype=torch.bfloat16, device=device)
+    wv = torch.empty_like(wk)
+    qsl = np.arange(0, requests * chunk + 1, chunk, dtype=np.int64)
+    seq = np.full(requests, total, np.int64)
+    group = plan_prefill_groups(work.block_table, 0, requests, qsl, seq, requests * pages, device)[0]
+
+    def fused() -> None:
+        prefill_attention(q, tabs, work.block_table, q_start, ctx_lens, SCALE, out_fused, chunk)
+
+    def two_step() -> None:
+        work.store.gather(0, group.src_blocks, wk, wv)
+        workspace_prefill_attention(q, wk, wv, group, SCALE, out_two)
+
+    def timed(fn, rounds: int) -> list[float]:
+        fn()
+        torch.cuda.synchronize()
+        samples = []
+        for _ in range(rounds):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            fn()
+            e1.record()
+            torch.cuda.synchronize()
+            samples.append(e0.elapsed_time(e1))
+        return samples
+
+    t_fused, t_two = timed(fused, 10), timed(two_step, 5)
+    status = prefill_status(device)
+    # fp32 causal attention over the kept source KV of request 0.
+    kv = work.sample[(0, 0)].float()
+    mask = torch.ones(chunk, total, dtype=torch.bool, device=device).tril(total - chunk)
+    small, large = [], []
+    for h in range(0, H, max(1, H // 4)):
+        s = (q[:chunk, h].float() @ kv[0][:, h].T) * SCALE
+        ref = torch.softmax(s.masked_fill(~mask, float("-inf")), -1) @ kv[1][:, h]
+        err = (out_fused[:chunk, h].float() - ref).abs()
+        big = ref.abs() > 1.0
+        small.append(err[~big])
+        large.append((err / ref.abs().clamp(min=1.0))[big])
+    small, large = torch.cat(small), torch.cat(large)
+    # Query i sees cached + i + 1 keys: 4 flops per (query, key, dim) for the two products.
+    flops = 4.0 * requests * H * G * 128 * (chunk * cached + chunk * (chunk + 1) / 2)
+    med_fused, med_two = float(np.median(t_fused)), float(np.median(t_two))
+    out = {
+        "workload": f"{cfg.name}: {requests} requests x ({cached} cached + {chunk} new tokens), "
+                    f"{H} KV heads, group {G}, one layer",
+        "fused_over_records": {"ms_per_layer": med_fused, "tflops": flops / (med_fused * 1e-3) / 1e12,
+                               "kernel": "prefill_attn_kernel (tcgen05, operands decoded in shared memory)"},
+        "decompress_then_attend": {"ms_per_layer": med_two, "tflops": flops / (med_two * 1e-3) / 1e12,
+                                   "kernels": "gather_kernel + torch SDPA per request"},
+        "speedup": med_two / med_fused,
+        "validation_vs_fp32_reference": {
+            "max_abs": float(small.max()), "mean_abs": float(small.mean()),
+            "max_rel_above_1": float(large.max()) if large.numel() else 0.0,
+            "mean_rel_above_1": float(large.mean()) if large.numel() else 0.0,
+            "outputs_above_1": int(large.numel())},
+        "max_abs_between_paths": float((out_fused.float() - out_two.float()).abs().max()),
+        "status_word": status,
+    }
+    del work, wk, wv
+    torch.cuda.empty_cache()
+    return out
+
+
 def brief(line: dict) -> dict:
     """The part of a decode result that the headline line carries for an extra workload."""
     keep = ("us_per_layer", "us_per_layer_median", "eager_us_per_layer", "value", "kv_ratio", "validation")
@@ -942,6 +1035,8 @@ def run_ours(args) -> dict:
     if args.workload == "c4":
         line = run_codec(args, args.junk if args.junk >= 0 else NEAR_LIMIT_JUNK, args.layers or 2)
         line.update({"metric": "block_encode_and_decompress_throughput", "n_gpus": 1})
+        if args.prefill_attention:
+            line["prefill_attention"] = run_prefill_attention(args)
         clocks.stop()
         env.close()
         return line
@@ -963,6 +1058,7 @@ def run_ours(args) -> dict:
         args.steps, args.warmup = keep
         extra["c4_prefill_as_written_junk_2pct"] = run_codec(args, 0.02)
         extra["c4_prefill_near_overflow_limit"] = run_codec(args, NEAR_LIMIT_JUNK)
+        extra["c4_prefill_attention"] = run_prefill_attention(args)
         line["extra"] = extra
     env.close()
     return line if env.rank == 0 else {}
@@ -1058,6 +1154,8 @@ def main() -> None:
     parser.add_argument("--junk", type=float, default=-1.0, help="c4: junk fraction")
     parser.add_argument("--overflow", type=int, default=8192, help="c4: overflow records")
     parser.add_argument("--codec-steps", type=int, default=5, help="c4: timed passes over the layers")
+    parser.add_argument("--prefill-attention", action="store_true",
+                        help="c4: also time prefill attention over compressed records")
     parser.add_argument("--gather", choices=("peers", "nccl"), default="peers",
                         help="N > 1: how the per-rank outputs reach every rank's o_proj input")
     parser.add_argument("--layers", type=int, default=0, help="resident layers (default: what fits)")

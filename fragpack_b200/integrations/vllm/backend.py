@@ -20,9 +20,12 @@ Two parts:
   imports vLLM.
 
 Differences from the reference, on purpose: compute capability 10 (B200)
-instead of 9; prefill attention over the workspace is torch SDPA per request
-(the reference calls vLLM's FlashAttention-3, which is SM90-only); the decode
-workspace is sized by this package's ``workspace_elems``.
+instead of 9; prefill rows are attended directly over the compressed records
+by :func:`fragpack_b200.ops.prefill_attn.prefill_attention` (the reference
+decompresses into the workspace and calls vLLM's FlashAttention-3, which is
+SM90-only; that two-step path is kept as ``run_layer(..., fused_prefill=False)``
+with torch SDPA per request in FlashAttention's place); the decode workspace
+is sized by this package's ``workspace_elems``.
 """
 
 from __future__ import annotations
@@ -43,6 +46,7 @@ from fragpack_b200.ops.fused_attn_decode import (
     workspace_elems,
 )
 from fragpack_b200.ops.hbm_kv import BLOCK_TOKENS, HEAD_DIM, HbmKvStore, page_bytes, register_store
+from fragpack_b200.ops.prefill_attn import prefill_attention as fused_prefill_attention
 
 _POLL_EVERY = 16
 _LOG_EVERY = 4096
@@ -59,6 +63,8 @@ class PrefillGroup:
     Attributes:
         src_blocks: int32 ``[P]`` blocks decoded into workspace pages ``0..P``.
         block_table: int32 ``[R, max_pages]`` workspace page ids per row.
+        store_block_table: int32 ``[R, max_pages]`` the rows' blocks in the store
+            (what the fused prefill kernel walks; the workspace is not used then).
         cu_seqlens_q: int32 ``[R + 1]`` query offsets relative to ``tok0``.
         seqused_k: int32 ``[R]`` context lengths.
         tok0: First token of the group in the batch.
@@ -69,6 +75,7 @@ class PrefillGroup:
 
     src_blocks: torch.Tensor
     block_table: torch.Tensor
+    store_block_table: torch.Tensor
     cu_seqlens_q: torch.Tensor
     seqused_k: torch.Tensor
     tok0: int
@@ -162,10 +169,12 @@ def plan_prefill_groups(
         a, b = total, 2 * total
         c = b + rows * width
         d = c + rows + 1
+        src_blocks = block_table[dev[:a], dev[a:b]].to(torch.int32)
         groups.append(
             PrefillGroup(
-                src_blocks=block_table[dev[:a], dev[a:b]].to(torch.int32),
+                src_blocks=src_blocks,
                 block_table=dev[b:c].view(rows, width).to(torch.int32),
+                store_block_table=src_blocks[dev[b:c]].view(rows, width).contiguous(),
                 cu_seqlens_q=dev[c:d].to(torch.int32),
                 seqused_k=dev[d:].to(torch.int32),
                 tok0=int(query_start[r0]),
@@ -229,6 +238,7 @@ def run_layer(
     output: torch.Tensor,
     scale: float,
     prefill_attention: Callable[..., None] = workspace_prefill_attention,
+    fused_prefill: bool = True,
 ) -> torch.Tensor:
     """One layer of a step: write new KV, attend, encode closed blocks (``backend.py:536-579``).
 
@@ -239,7 +249,11 @@ def run_layer(
         key, value: BF16 ``[T, H, 128]`` new tokens.
         output: BF16 ``[T, Hq, 128]`` output buffer.
         scale: Softmax scale.
-        prefill_attention: ``(query, wk, wv, group, scale, out)`` for one prefill group.
+        prefill_attention: ``(query, wk, wv, group, scale, out)`` for one prefill group
+            over the decompressed workspace (used when ``fused_prefill`` is false).
+        fused_prefill: Attend prefill rows directly over the compressed records
+            (one tensor-core kernel per group, no workspace) instead of
+            decompressing into the workspace first.
 
     Returns:
         ``output``.
@@ -257,6 +271,13 @@ def run_layer(
             md.units, output[:nd], md.decode_workspace, replan=layer == 0,
         )
     for group in md.prefills:
+        if fused_prefill:
+            fused_prefill_attention(
+                query[group.tok0 : group.tok1], md.layer_tables[layer], group.store_block_table,
+                group.cu_seqlens_q, group.seqused_k, scale, output[group.tok0 : group.tok1],
+                group.max_seqlen_q,
+            )
+            continue
         store.gather(layer, group.src_blocks, md.wk, md.wv)
         prefill_attention(query[group.tok0 : group.tok1], md.wk, md.wv, group, scale,
                           output[group.tok0 : group.tok1])

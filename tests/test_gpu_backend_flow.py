@@ -54,7 +54,9 @@ def _reference(q, k, v, n_new):
     return out
 
 
-def test_chunked_prefill_then_decode_matches_fp32_attention() -> None:
+@pytest.mark.parametrize("fused_prefill", [True, False])
+def test_chunked_prefill_then_decode_matches_fp32_attention(fused_prefill: bool) -> None:
+    """Prefill rows over the compressed records (one kernel) or over the decompressed workspace."""
     device = torch.device("cuda", torch.cuda.current_device())
     gen = torch.Generator().manual_seed(41)
     sample = (torch.randn(8, L, 2, T, H, D, generator=gen) * 0.5).to(torch.bfloat16)
@@ -113,7 +115,8 @@ def test_chunked_prefill_then_decode_matches_fp32_attention() -> None:
             k = (torch.randn(total, H, D, generator=gen) * 0.5).to(torch.bfloat16)
             v = (torch.randn(total, H, D, generator=gen) * 0.5).to(torch.bfloat16)
             out = torch.full((total, HQ, D), float("nan"), dtype=torch.bfloat16, device=device)
-            run_layer(md, layer, q.to(device), k.to(device), v.to(device), out, SCALE)
+            run_layer(md, layer, q.to(device), k.to(device), v.to(device), out, SCALE,
+                      fused_prefill=fused_prefill)
             got = out.float().cpu()
             for i, (r, n) in enumerate(ordered):
                 t0, t1 = int(qsl[i]), int(qsl[i + 1])
