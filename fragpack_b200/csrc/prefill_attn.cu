@@ -5,11 +5,11 @@
 // (fragpack/integrations/vllm/backend.py:560-575: store.gather, then
 // flash_attn_varlen_func with causal=True and a paged workspace).  This kernel
 // does both in one pass and never writes the decompressed KV to HBM: a CTA
-// takes 128 query rows (128 / G tokens x the G query heads of one KV head),
-// walks the request's pages, decodes each K and V record straight into
-// shared-memory tiles laid out as tensor-core operands, and runs both products
-// on the 5th-generation tensor cores (tcgen05.mma, accumulators in tensor
-// memory):
+// takes two tiles of 128 query rows (128 / G tokens x the G query heads of one
+// KV head each; a decoded record serves both), walks the request's pages,
+// decodes each K and V record straight into shared-memory tiles laid out as
+// tensor-core operands, and runs both products on the 5th-generation tensor
+// cores (tcgen05.mma, accumulators in tensor memory), per query tile:
 //
 //   S = Q K^T      A = Q tile [128 rows, 128 dims], B = K tile [128 tokens, 128 dims]
 //   O += P V       A = P tile [128 rows, 128 tokens], B = V tile [128 dims, 128 tokens]
@@ -17,11 +17,12 @@
 // All four tiles are K-major with the 128-byte swizzle (eight 16-byte chunks
 // of a row XOR-ed with the row index modulo 8), which is also what stmatrix
 // can write from the record decoder's mma fragments: a K record yields rows =
-// tokens, a V record rows = dims, with the same store.  S lives in tensor
-// memory columns 0..127, O in columns 128..255; four warps read S with
-// tcgen05.ld, one thread per query row (no shuffles in the softmax), write P
-// as BF16 into its operand tile, and rescale O in tensor memory when a row's
-// maximum rose.  P is rounded to BF16 and the denominator sums the unrounded
+// tokens, a V record rows = dims, with the same store.  The two S tiles live in
+// tensor memory columns 0..255, the two O tiles in columns 256..511; each
+// warpgroup (four warps) owns one query tile and reads its S with tcgen05.ld,
+// one thread per query row (no shuffles in the softmax), writes P as BF16 into
+// its operand tile, and rescales its O in tensor memory when a row's maximum
+// rose.  P is rounded to BF16 and the denominator sums the unrounded
 // values, as in decode attention.
 //
 // This first version runs its phases one after another (decode K, S product,
@@ -37,17 +38,18 @@
 namespace fpb {
 namespace {
 
-constexpr int kPrefillThreads = 256;  // eight warps decode; warps 0-3 also run the softmax
+constexpr int kPrefillThreads = 256;  // eight warps decode; each warpgroup runs one tile's softmax
 constexpr int kTile = 128;
+constexpr int kQTiles = 2;                     // query tiles per CTA, one per warpgroup
 constexpr int kTileBytes = kTile * kTile * 2;  // 32 KB: one operand tile
 constexpr int kHalfTile = kTileBytes / 2;      // one 64-column (128-byte) swizzle atom column
-constexpr uint32_t kTmemColumns = 256;         // S: 0..127, O: 128..255
+constexpr uint32_t kTmemColumns = 512;         // S tiles: 0..255, O tiles: 256..511
 
 struct PrefillSmem {
-  __align__(1024) uint8_t q[kTileBytes];
+  __align__(1024) uint8_t q[kQTiles][kTileBytes];
   __align__(1024) uint8_t k[kTileBytes];
   __align__(1024) uint8_t v[kTileBytes];
-  __align__(1024) uint8_t p[kTileBytes];
+  __align__(1024) uint8_t p[kQTiles][kTileBytes];
   __align__(16) uint8_t esc[kEscBytes];
   __align__(8) uint64_t bar_s;  // S product complete
   __align__(8) uint64_t bar_o;  // O product complete
@@ -197,12 +199,19 @@ __global__ void __launch_bounds__(kPrefillThreads, 1) prefill_attn_kernel(Prefil
   const int req = blockIdx.z, head = blockIdx.y;
   const int rows_tokens = kTile / p.group;  // query tokens per tile
   const int q0 = p.q_start[req], n_q = p.q_start[req + 1] - q0;
-  const int tok0 = blockIdx.x * rows_tokens;
-  if (tok0 >= n_q) return;  // uniform over the CTA, before anything is allocated
+  const int cta_tok0 = blockIdx.x * kQTiles * rows_tokens;
+  if (cta_tok0 >= n_q) return;  // uniform over the CTA, before anything is allocated
   const int ctx = p.ctx_len[req];
   const int first_pos = ctx - n_q;  // position of the request's first query token
-  const int tile_tokens = min(rows_tokens, n_q - tok0);
-  const int last_page = (first_pos + tok0 + tile_tokens - 1) >> 7;
+  // Last page each query tile needs (-1: the tile lies past the request's
+  // queries); the CTA walks the pages of its last tile.
+  int tile_last[kQTiles];
+#pragma unroll
+  for (int t = 0; t < kQTiles; ++t) {
+    const int t0 = cta_tok0 + t * rows_tokens;
+    tile_last[t] = t0 < n_q ? (first_pos + min(t0 + rows_tokens, n_q) - 1) >> 7 : -1;
+  }
+  const int last_page = max(tile_last[0], tile_last[kQTiles - 1]);
 
   if (tid == 0) {
     mbar_init(&sm.bar_s, 1);
@@ -220,39 +229,43 @@ __global__ void __launch_bounds__(kPrefillThreads, 1) prefill_attn_kernel(Prefil
                  : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
-  // Q tile: row = token * G + head of the group, zero rows past the request's queries.
-  for (int x = tid; x < kTile * 16; x += kPrefillThreads) {
-    const int row = x >> 4, col = (x & 15) * 8;
-    const int tok = tok0 + row / p.group, g = row % p.group;
+  // Q tiles: row = token * G + head of the group, zero rows past the request's queries.
+  for (int x = tid; x < kQTiles * kTile * 16; x += kPrefillThreads) {
+    const int t = x / (kTile * 16), row = (x >> 4) & (kTile - 1), col = (x & 15) * 8;
+    const int tok = cta_tok0 + t * rows_tokens + row / p.group, g = row % p.group;
     uint4 val = make_uint4(0u, 0u, 0u, 0u);
     if (tok < n_q)
       val = *reinterpret_cast<const uint4*>(p.q + (int64_t)(q0 + tok) * p.q_stride +
                                             (int64_t)(head * p.group + g) * 128 + col);
-    *reinterpret_cast<uint4*>(sm.q + tile_chunk(row, col)) = val;
+    *reinterpret_cast<uint4*>(sm.q[t] + tile_chunk(row, col)) = val;
   }
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const uint32_t tmem = sm.tmem_base;
-  const uint32_t tmem_s = tmem, tmem_o = tmem + (uint32_t)kTile;
   const HeadTables tab_k = load_tables(p.plut, p.slut, head);
   const HeadTables tab_v = load_tables(p.plut, p.slut, p.kvh + head);
   const int32_t* bt = p.block_table + (int64_t)req * p.bt_stride;
 
-  // Softmax state of this thread's query row (warps 0-3: row = tid).
-  const int row = tid & (kTile - 1);
-  // Key positions <= row_pos are visible (rows past the request's queries
-  // compute like its last token and are not stored).
+  // Softmax state of this thread's query row: warpgroup `mine` owns query tile
+  // `mine`, thread = row.  Key positions <= row_pos are visible (rows past the
+  // request's queries compute like its last token and are not stored).
+  const int mine = warp >> 2, row = tid & (kTile - 1);
+  const int tok0 = cta_tok0 + mine * rows_tokens;
+  const int my_last = mine == 0 ? tile_last[0] : tile_last[kQTiles - 1];
   const int row_pos = min(first_pos + tok0 + row / p.group, ctx - 1);
   float row_max = -INFINITY, row_sum = 0.f;
   const uint32_t lane_base = (uint32_t)(32 * (warp & 3)) << 16;  // this warp's tensor-memory lanes
+  const uint32_t tmem_s = tmem + (uint32_t)(mine * kTile);
+  const uint32_t tmem_o = tmem + (uint32_t)((kQTiles + mine) * kTile);
+  uint8_t* p_tile = sm.p[mine];
 
   for (int page = 0; page <= last_page; ++page) {
     const uint32_t parity = (uint32_t)page & 1u;
     const int64_t idx = (int64_t)bt[page] * 2 * p.kvh + head;
     const int open_cols = ctx - page * kTile;  // tokens of this block that exist
-    // ---- K record -> K tile (its previous reader, the S product of the page
+    // ---- K record -> K tile (its previous readers, the S products of the page
     // before, finished before that page's softmax began).
     record_to_tile(reinterpret_cast<const uint8_t*>(p.rec_addr[idx]), p.rec_len[idx], tab_k, sm.k,
                    sm.esc, tid, p.k, kTile);
@@ -260,16 +273,20 @@ __global__ void __launch_bounds__(kPrefillThreads, 1) prefill_attn_kernel(Prefil
     __syncthreads();
     if (tid == 0) {
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      tile_product(tmem_s, smem_addr(sm.q), smem_addr(sm.k), false);
+#pragma unroll
+      for (int t = 0; t < kQTiles; ++t)
+        if (page <= tile_last[t])
+          tile_product(tmem + (uint32_t)(t * kTile), smem_addr(sm.q[t]), smem_addr(sm.k), false);
       umma_commit(&sm.bar_s);
     }
-    // ---- V record -> V tile while the S product runs; the O product of the
+    // ---- V record -> V tile while the S products run; the O products of the
     // page before must be done with the V and P tiles (and with O) first.
     if (page > 0) bounded_wait(&sm.bar_o, parity ^ 1u, &sm.wait);
     record_to_tile(reinterpret_cast<const uint8_t*>(p.rec_addr[idx + p.kvh]),
                    p.rec_len[idx + p.kvh], tab_v, sm.v, sm.esc, tid, p.k, open_cols);
-    // ---- softmax: one thread per query row.
-    if (warp < 4) {
+    // ---- softmax: one thread per query row of the warpgroup's tile (a tile
+    // whose queries all lie before this page has nothing to add).
+    if (page <= my_last) {
       bounded_wait(&sm.bar_s, parity, &sm.wait);
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       const int visible = row_pos - page * kTile;  // columns 0..visible of this page count
@@ -313,7 +330,7 @@ __global__ void __launch_bounds__(kPrefillThreads, 1) prefill_attn_kernel(Prefil
         }
 #pragma unroll
         for (int ch = 0; ch < 4; ++ch)
-          *reinterpret_cast<uint4*>(sm.p + tile_chunk(row, c0 + 8 * ch)) =
+          *reinterpret_cast<uint4*>(p_tile + tile_chunk(row, c0 + 8 * ch)) =
               make_uint4(packed[4 * ch], packed[4 * ch + 1], packed[4 * ch + 2], packed[4 * ch + 3]);
       }
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -322,13 +339,17 @@ __global__ void __launch_bounds__(kPrefillThreads, 1) prefill_attn_kernel(Prefil
     __syncthreads();  // V and P tiles complete, S read, O rescaled
     if (tid == 0) {
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      tile_product(tmem_o, smem_addr(sm.p), smem_addr(sm.v), page > 0);
+#pragma unroll
+      for (int t = 0; t < kQTiles; ++t)
+        if (page <= tile_last[t])
+          tile_product(tmem + (uint32_t)((kQTiles + t) * kTile), smem_addr(sm.p[t]), smem_addr(sm.v),
+                       page > 0);
       umma_commit(&sm.bar_o);
     }
   }
 
   // ---- epilogue: O / row_sum -> BF16 rows of `out`.
-  if (warp < 4) {
+  if (my_last >= 0) {
     bounded_wait(&sm.bar_o, (uint32_t)last_page & 1u, &sm.wait);
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const int tok = tok0 + row / p.group, g = row % p.group;
@@ -414,8 +435,8 @@ int fp_prefill_attention(const void* q, int64_t q_stride, const int64_t* rec_add
   p.scale_log2 = scale * 1.4426950408889634f;
   p.k = pipe_consts();
   p.wait_limit = wait_debug().limit;
-  const int rows_tokens = kTile / group;
-  const dim3 grid((unsigned)((max_query_tokens + rows_tokens - 1) / rows_tokens), (unsigned)kv_heads,
+  const int cta_tokens = kQTiles * (kTile / group);  // query tokens per CTA
+  const dim3 grid((unsigned)((max_query_tokens + cta_tokens - 1) / cta_tokens), (unsigned)kv_heads,
                   (unsigned)num_requests);
   prefill_attn_kernel<<<grid, kPrefillThreads, smem, (cudaStream_t)stream>>>(p);
   FP_LAUNCH_CHECK("prefill_attn_kernel");
