@@ -265,6 +265,15 @@ __global__ void __launch_bounds__(kPrefillThreads, 1) prefill_attn_kernel(Prefil
     const uint32_t parity = (uint32_t)page & 1u;
     const int64_t idx = (int64_t)bt[page] * 2 * p.kvh + head;
     const int open_cols = ctx - page * kTile;  // tokens of this block that exist
+    if (tid < 2 && page < last_page) {
+      // The records are decoded straight from global memory: ask the L2 for the
+      // next page's K (thread 0) and V (thread 1) record while this page is worked on.
+      const int64_t next = (int64_t)bt[page + 1] * 2 * p.kvh + head + tid * p.kvh;
+      const int32_t n = p.rec_len[next];
+      prefetch_l2(reinterpret_cast<const void*>(p.rec_addr[next]),
+                  n > kVarCap || n < kHeaderBytes ? (uint32_t)kRawRecord
+                                                  : (uint32_t)(kDenseBytes + (n & ~15)));
+    }
     // ---- K record -> K tile (its previous readers, the S products of the page
     // before, finished before that page's softmax began).
     record_to_tile(reinterpret_cast<const uint8_t*>(p.rec_addr[idx]), p.rec_len[idx], tab_k, sm.k,
