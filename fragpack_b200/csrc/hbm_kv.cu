@@ -204,13 +204,15 @@ write_kernel(StoreView v, const uint16_t* key, const uint16_t* value, int64_t ks
 struct EncodeShared {
   __align__(16) uint8_t var[kVarCap];
   // Per byte position k of a packed word and per high byte: .x = the 3-bit
-  // primary code (7 = escape) already at nibble k, .y = the escape nibble
-  // (rank - 7, or 15 for a byte outside the table) already at byte k.  Four
-  // look-ups OR into the packed codes and the escape bytes of four scalars
-  // with no shifting or repacking afterwards.
+  // primary code (7 = escape) already at nibble k, plus an escape flag at bit
+  // 16 + k; .y = the escape nibble (rank - 7, or 15 for a byte outside the
+  // table) already at byte k.  Four look-ups OR into the packed codes, the
+  // escape mask and the escape bytes of four scalars with no shifting or
+  // repacking afterwards.
   __align__(16) uint2 classes[4][256];
-  // Per 8-bit flag mask: byte selectors (prmt nibbles) listing the flagged
-  // positions in ascending order; unused selectors are 0.
+  // Per 8-bit escape mask: byte selectors (prmt nibbles) listing the flagged
+  // positions in ascending order; unused selectors are 8, which makes prmt
+  // replicate the sign bit of an escape byte (always clear): a zero byte.
   uint32_t compact[256];
   int warp_sum[2][8];
   uint8_t* dst;
@@ -234,11 +236,15 @@ __device__ __forceinline__ void load_classes(EncodeShared& sh, const uint8_t* ra
   const uint32_t nib = r < kPrimaryDirect ? 0u : (r < kTableEntries ? r - kPrimaryDirect : 15u);
 #pragma unroll
   for (int k = 0; k < 4; ++k)
-    sh.classes[k][table_slot((uint32_t)tid)] = make_uint2(code << (4 * k), nib << (8 * k));
-  uint32_t pick = 0;
-  int k = 0;
+    sh.classes[k][table_slot((uint32_t)tid)] =
+        make_uint2((code << (4 * k)) | ((uint32_t)(r >= kPrimaryDirect) << (16 + k)), nib << (8 * k));
+  uint32_t pick = 0x88888888u;
+  int n = 0;
   for (int pos = 0; pos < 8; ++pos)
-    if ((tid >> pos) & 1) pick |= (uint32_t)pos << (4 * k++);
+    if ((tid >> pos) & 1) {
+      pick ^= (8u ^ (uint32_t)pos) << (4 * n);
+      ++n;
+    }
   sh.compact[tid] = pick;
 }
 
@@ -249,28 +255,38 @@ struct EncodePlan {
 
 // Classes of the four high bytes packed in `hi`: .x = their primary codes as
 // four nibbles, .y = their escape nibbles as four bytes.
-__device__ __forceinline__ uint2 classes4(const EncodeShared& sh, uint32_t hi) {
+__device__ __forceinline__ uint2 classes4(const EncodeShared& sh, uint32_t hi, const PipeConsts& k) {
   // All four bytes rotated at once (see table_slot).
   const uint32_t at = ((hi << 1) & 0xfefefefeu) | ((hi >> 7) & 0x01010101u);
   const uint2 c0 = sh.classes[0][at & 0xffu], c1 = sh.classes[1][(at >> 8) & 0xffu];
   const uint2 c2 = sh.classes[2][(at >> 16) & 0xffu], c3 = sh.classes[3][at >> 24];
-  return make_uint2(c0.x | c1.x | c2.x | c3.x, c0.y | c1.y | c2.y | c3.y);
+  // The four entries occupy disjoint bits, so their OR is their sum: written
+  // as multiply-adds, it issues on the multiply pipe instead of the half-rate
+  // integer pipe that the rest of the classification keeps busy.
+  return make_uint2(add_fma(add_fma(c0.x, c1.x, k), add_fma(c2.x, c3.x, k), k),
+                    add_fma(add_fma(c0.y, c1.y, k), add_fma(c2.y, c3.y, k), k));
 }
 
 // `place(plan, raw)` is called by all lanes of warp 0 together and returns, in
 // every lane, where the record goes; it sets `raw` when the record must be
 // stored raw (it does not code, or it codes but no longer fits its page); a
 // null destination drops the record.
-template <typename Place>
+//
+// `wd` is only read while the scalars are classified (the low bytes are set
+// aside in packed form as each word is consumed, so the 32 registers of the
+// record do not stay live to the end); the rare paths that need the original
+// words again - more escapes than the queue holds, a raw store - fetch them
+// with `reload(st)`.
+template <typename Reload, typename Place>
 __device__ __forceinline__ void encode_cta(const uint4 (&wd)[8], EncodeShared& sh, int tid,
-                                           Place&& place) {
+                                           const PipeConsts& k, Reload&& reload, Place&& place) {
   const int lane = tid & 31, warp = tid >> 5;
   for (int i = tid; i < kVarCap / 16; i += kOwners)
     reinterpret_cast<uint4*>(sh.var)[i] = make_uint4(0, 0, 0, 0);
 
   // Classify the 64 scalars four at a time: primary codes as nibble words,
   // escape nibbles appended to a queue (first 16; longer runs are redone below).
-  uint32_t codes[8];
+  uint32_t codes[8], low[16];
   uint64_t queue = 0;
   uint32_t raw_q[4] = {0, 0, 0, 0};  // first raw entries: local ordinal | high << 16
   int n_esc = 0, n_raw = 0;
@@ -278,24 +294,20 @@ __device__ __forceinline__ void encode_cta(const uint4 (&wd)[8], EncodeShared& s
   for (int st = 0; st < 8; ++st) {
     const uint32_t hi_a = __byte_perm(wd[st].x, wd[st].y, 0x7531);
     const uint32_t hi_b = __byte_perm(wd[st].z, wd[st].w, 0x7531);
-    const uint2 ca = classes4(sh, hi_a), cb = classes4(sh, hi_b);
-    codes[st] = ca.x | (cb.x << 16);
-    const uint32_t f = (codes[st] + 0x11111111u) & 0x88888888u;  // nibbles equal to 7
+    low[2 * st] = __byte_perm(wd[st].x, wd[st].y, 0x6420);
+    low[2 * st + 1] = __byte_perm(wd[st].z, wd[st].w, 0x6420);
+    const uint2 ca = classes4(sh, hi_a, k), cb = classes4(sh, hi_b, k);
+    codes[st] = prmt(ca.x, cb.x, 0x5410u);
     // This word's escape nibbles, in order, without a loop over them (lanes
     // differ in how many they have; a loop runs as long as the worst lane).
-    // Flags -> one byte: the multiply moves flag i of each half to bit 12 + i /
-    // 28 + i; no two partial products meet, so nothing carries.
-    const uint32_t gathered = (f >> 3) * 0x1248u;
-    const uint32_t mask8 = ((gathered >> 12) & 0xfu) | ((gathered >> 24) & 0xf0u);
+    const uint32_t mask8 = (ca.x >> 16) | ((cb.x >> 12) & 0xf0u);
     const uint32_t pick = sh.compact[mask8];  // byte selectors that move flagged bytes to the front
-    const uint32_t front_lo = __byte_perm(ca.y, cb.y, pick), front_hi = __byte_perm(ca.y, cb.y, pick >> 16);
-    const int here = __popc(f);
+    const uint32_t front_lo = prmt(ca.y, cb.y, pick), front_hi = prmt(ca.y, cb.y, pick >> 16);
+    const int here = __popc(mask8);
     // Eight bytes holding one nibble each -> eight adjacent nibbles: OR-ing a
     // word with itself shifted by four pairs the nibbles up in bytes 0 and 2.
     const uint32_t pair_lo = front_lo | (front_lo >> 4), pair_hi = front_hi | (front_hi >> 4);
-    uint32_t packed = __byte_perm(pair_lo, pair_hi, 0x6420);
-    // Drop what the padding selected (a shift count of 32 gives 0).
-    packed &= __funnelshift_rc(0xffffffffu, 0u, 32 - 4 * here);
+    const uint32_t packed = prmt(pair_lo, pair_hi, 0x6420u);
     if (n_esc < 16) queue |= (uint64_t)packed << (4 * n_esc);
     // Raw scalars (nibble 15) are rare.
     uint32_t raws = packed & (packed >> 1);
@@ -303,10 +315,10 @@ __device__ __forceinline__ void encode_cta(const uint4 (&wd)[8], EncodeShared& s
     if (raws) {
       const uint32_t high_lo = __byte_perm(hi_a, hi_b, pick), high_hi = __byte_perm(hi_a, hi_b, pick >> 16);
       do {
-        const int k = (__ffs(raws) - 1) >> 2;
+        const int at = (__ffs(raws) - 1) >> 2;
         raws &= raws - 1;
-        const uint32_t high = ((k < 4 ? high_lo : high_hi) >> (8 * (k & 3))) & 0xffu;
-        const uint32_t entry = (uint32_t)(n_esc + k) | (high << 16);
+        const uint32_t high = ((at < 4 ? high_lo : high_hi) >> (8 * (at & 3))) & 0xffu;
+        const uint32_t entry = (uint32_t)(n_esc + at) | (high << 16);
 #pragma unroll
         for (int x = 0; x < 4; ++x)
           if (n_raw == x) raw_q[x] = entry;
@@ -383,13 +395,13 @@ __device__ __forceinline__ void encode_cta(const uint4 (&wd)[8], EncodeShared& s
     int ordinal = esc_at;
 #pragma unroll
     for (int st = 0; st < 8; ++st) {
-      const uint32_t highs[2] = {__byte_perm(wd[st].x, wd[st].y, 0x7531),
-                                 __byte_perm(wd[st].z, wd[st].w, 0x7531)};
+      const uint4 w = reload(st);
+      const uint32_t highs[2] = {__byte_perm(w.x, w.y, 0x7531), __byte_perm(w.z, w.w, 0x7531)};
 #pragma unroll
       for (int e = 0; e < 8; ++e) {
         const uint32_t high = (highs[e >> 2] >> (8 * (e & 3))) & 0xffu;
         const uint2 c = sh.classes[0][table_slot(high)];
-        if (c.x == (uint32_t)kPrimaryDirect) {
+        if ((c.x & 0xfu) == (uint32_t)kPrimaryDirect) {
           const uint32_t nib = c.y;
           if (n_esc > 16) {
             const int bit = 8 * kHeaderBytes + 4 * ordinal;
@@ -420,18 +432,15 @@ __device__ __forceinline__ void encode_cta(const uint4 (&wd)[8], EncodeShared& s
   if (dst == nullptr) return;
   if (sh.raw) {
 #pragma unroll
-    for (int st = 0; st < 8; ++st) reinterpret_cast<uint4*>(dst)[st * kOwners + tid] = wd[st];
+    for (int st = 0; st < 8; ++st) reinterpret_cast<uint4*>(dst)[st * kOwners + tid] = reload(st);
     return;
   }
   // Dense part: low bytes in four 16-byte chunks, symbols in three 8-byte
   // chunks, both chunk-major (attn_page.py:272-276).
 #pragma unroll
-  for (int j = 0; j < 4; ++j) {
-    const uint4 a = wd[2 * j], b = wd[2 * j + 1];
+  for (int j = 0; j < 4; ++j)
     reinterpret_cast<uint4*>(dst)[j * kOwners + tid] =
-        make_uint4(__byte_perm(a.x, a.y, 0x6420), __byte_perm(a.z, a.w, 0x6420),
-                   __byte_perm(b.x, b.y, 0x6420), __byte_perm(b.z, b.w, 0x6420));
-  }
+        make_uint4(low[4 * j], low[4 * j + 1], low[4 * j + 2], low[4 * j + 3]);
 #pragma unroll
   for (int m = 0; m < 3; ++m)
     reinterpret_cast<uint2*>(dst + kLowBytes)[m * kOwners + tid] =
@@ -442,8 +451,12 @@ __device__ __forceinline__ void encode_cta(const uint4 (&wd)[8], EncodeShared& s
 
 // grid (max_close, 2 H): CTA (i, rec) encodes record `rec` of close_list[i]
 // at `layer` from staging.  hbm_kv.cu:257-429.
-__global__ void __launch_bounds__(kOwners, 3)
-encode_kernel(StoreView v, int layer, uint8_t* arena, int64_t page_bytes, const uint8_t* rank_of) {
+// Four CTAs per SM (64 registers): the kernel's stalls are the load at a CTA's
+// start and the placement's atomic at its end, which only other resident CTAs
+// cover; a fourth CTA measured 12 % faster than three.
+__global__ void __launch_bounds__(kOwners, 4)
+encode_kernel(StoreView v, int layer, uint8_t* arena, int64_t page_bytes, const uint8_t* rank_of,
+              PipeConsts k) {
   __shared__ EncodeShared sh;
   const fp_store& s = v.s;
   if ((int)blockIdx.x >= s.counters[FP_CTR_CLOSES]) return;
@@ -455,19 +468,9 @@ encode_kernel(StoreView v, int layer, uint8_t* arena, int64_t page_bytes, const 
   uint4 wd[8];
 #pragma unroll
   for (int st = 0; st < 8; ++st) wd[st] = reinterpret_cast<const uint4*>(src)[st * kOwners + tid];
-  // A closing block that donates its slot: the heir's transient record moves
-  // in (each owner overwrites only the words it has just read) and the heir's
-  // table entry follows it.  Attention has already read the transient copy.
-  const int heir = s.close_list[s.cap + blockIdx.x];
-  if (heir >= 0) {
-    const uint4* from = reinterpret_cast<const uint4*>(v.staging(s.wslot[heir], layer, rec));
-#pragma unroll
-    for (int st = 0; st < 8; ++st)
-      reinterpret_cast<uint4*>(src)[st * kOwners + tid] = from[st * kOwners + tid];
-    if (tid == 0) s.rec_addr[v.table_index(layer, heir, rec)] = reinterpret_cast<int64_t>(src);
-  }
   __syncthreads();
-  encode_cta(wd, sh, tid, [&](const EncodePlan& plan, bool& raw) -> uint8_t* {
+  const auto reload = [&](int st) { return reinterpret_cast<const uint4*>(src)[st * kOwners + tid]; };
+  encode_cta(wd, sh, tid, k, reload, [&](const EncodePlan& plan, bool& raw) -> uint8_t* {
     const int lane = tid & 31;
     int at = -1;
     if (lane == 0) {
@@ -529,6 +532,18 @@ encode_kernel(StoreView v, int layer, uint8_t* arena, int64_t page_bytes, const 
     }
     return dst;
   });
+  // A closing block that donates its slot: the heir's transient record moves
+  // in and the heir's table entry follows it.  Every owner overwrites only the
+  // words it alone read (and may have read again just above), so no barrier is
+  // needed; attention has already read the transient copy.
+  const int heir = s.close_list[s.cap + blockIdx.x];
+  if (heir >= 0) {
+    const uint4* from = reinterpret_cast<const uint4*>(v.staging(s.wslot[heir], layer, rec));
+#pragma unroll
+    for (int st = 0; st < 8; ++st)
+      reinterpret_cast<uint4*>(src)[st * kOwners + tid] = from[st * kOwners + tid];
+    if (tid == 0) s.rec_addr[v.table_index(layer, heir, rec)] = reinterpret_cast<int64_t>(src);
+  }
 }
 
 // Loads a token-major [128,128] BF16 tile (row stride `row_bytes`) into the
@@ -553,25 +568,21 @@ __device__ __forceinline__ void tile_store(const uint8_t* tile, uint8_t* dst, in
   }
 }
 
-// Fragment words of owner `tid` out of a token-major shared tile.
-__device__ __forceinline__ void tile_to_words(uint8_t* tile, int kv, int tid, uint4 (&wd)[8]) {
-  const OwnerCoords o(tid);
+// Fragment word `st` of owner `o` out of a token-major shared tile.
+__device__ __forceinline__ uint4 tile_word(uint8_t* tile, int kv, const OwnerCoords& o, int st) {
+  uint32_t w[4];
 #pragma unroll
-  for (int st = 0; st < 8; ++st) {
-    uint32_t w[4];
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const int j = i >> 1, f = i & 1;
-      if (kv == 0) {
-        w[i] = *reinterpret_cast<const uint32_t*>(tile_at(tile, o.row(j), o.col(st, f)));
-      } else {
-        const int tok = o.col(st, f), dim = o.row(j);
-        w[i] = (uint32_t)*reinterpret_cast<const uint16_t*>(tile_at(tile, tok, dim)) |
-               ((uint32_t)*reinterpret_cast<const uint16_t*>(tile_at(tile, tok + 1, dim)) << 16);
-      }
+  for (int i = 0; i < 4; ++i) {
+    const int j = i >> 1, f = i & 1;
+    if (kv == 0) {
+      w[i] = *reinterpret_cast<const uint32_t*>(tile_at(tile, o.row(j), o.col(st, f)));
+    } else {
+      const int tok = o.col(st, f), dim = o.row(j);
+      w[i] = (uint32_t)*reinterpret_cast<const uint16_t*>(tile_at(tile, tok, dim)) |
+             ((uint32_t)*reinterpret_cast<const uint16_t*>(tile_at(tile, tok + 1, dim)) << 16);
     }
-    wd[st] = make_uint4(w[0], w[1], w[2], w[3]);
   }
+  return make_uint4(w[0], w[1], w[2], w[3]);
 }
 
 __device__ __forceinline__ void word_to_tile(uint8_t* tile, int kv, const OwnerCoords& o, int st,
@@ -601,7 +612,8 @@ constexpr int kTileBytes = 128 * 256;
 // Batch encoder over token-major records: grid = records.
 __global__ void __launch_bounds__(kOwners, 3)
 encode_records_kernel(const uint8_t* raw, const uint8_t* rank_of, const int32_t* table_index,
-                      const int32_t* kv, uint8_t* out, int64_t out_stride, int32_t* out_len) {
+                      const int32_t* kv, uint8_t* out, int64_t out_stride, int32_t* out_len,
+                      PipeConsts k) {
   extern __shared__ __align__(16) uint8_t dyn[];
   uint8_t* tile = dyn;
   EncodeShared& sh = *reinterpret_cast<EncodeShared*>(dyn + kTileBytes);
@@ -611,10 +623,13 @@ encode_records_kernel(const uint8_t* raw, const uint8_t* rank_of, const int32_t*
   load_classes(sh, rank_of + (int64_t)(table_index ? table_index[i] : (int32_t)i) * 256, tid);
   tile_load(tile, raw + i * kRawRecord, 256, tid);
   __syncthreads();
+  const OwnerCoords o(tid);
   uint4 wd[8];
-  tile_to_words(tile, which, tid, wd);
+#pragma unroll
+  for (int st = 0; st < 8; ++st) wd[st] = tile_word(tile, which, o, st);
+  const auto reload = [&](int st) { return tile_word(tile, which, o, st); };
   uint8_t* dst = out + i * out_stride;
-  encode_cta(wd, sh, tid, [&](const EncodePlan& plan, bool& raw_out) -> uint8_t* {
+  encode_cta(wd, sh, tid, k, reload, [&](const EncodePlan& plan, bool& raw_out) -> uint8_t* {
     raw_out = !plan.codes;
     out_len[i] = plan.codes ? kDenseBytes + plan.var_len : kRawRecord;
     return dst;
@@ -858,7 +873,7 @@ int fp_hbm_encode(const fp_store* store, const uint8_t* rank_of, int32_t layer, 
   FP_REQUIRE(reinterpret_cast<uintptr_t>(arena) % 16 == 0, "arena must be 16-byte aligned");
   StoreView v{*store};
   encode_kernel<<<dim3((unsigned)max_close, 2 * store->H), kOwners, 0, (cudaStream_t)stream>>>(
-      v, layer, arena, page_bytes, rank_of);
+      v, layer, arena, page_bytes, rank_of, pipe_consts());
   FP_LAUNCH_CHECK("encode_kernel");
   return FP_OK;
 }
@@ -932,7 +947,8 @@ int fp_encode_records(const void* raw, int64_t n, const uint8_t* rank_of,
   static std::atomic<uint64_t> smem_allowed;
   if (int rc = allow_dynamic_smem(encode_records_kernel, smem, smem_allowed)) return rc;
   encode_records_kernel<<<(unsigned)n, kOwners, smem, (cudaStream_t)stream>>>(
-      static_cast<const uint8_t*>(raw), rank_of, table_index, kv, out, out_stride, out_len);
+      static_cast<const uint8_t*>(raw), rank_of, table_index, kv, out, out_stride, out_len,
+      pipe_consts());
   FP_LAUNCH_CHECK("encode_records_kernel");
   return FP_OK;
 }
