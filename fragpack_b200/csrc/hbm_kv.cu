@@ -205,8 +205,9 @@ struct EncodeShared {
   __align__(16) uint8_t var[kVarCap];
   // Per byte position k of a packed word and per high byte: .x = the 3-bit
   // primary code (7 = escape) already at nibble k, plus an escape flag at bit
-  // 16 + k; .y = the escape nibble (rank - 7, or 15 for a byte outside the
-  // table) already at byte k.  Four look-ups OR into the packed codes, the
+  // 16 + k and a flag for a byte outside the table at bit 24 + k; .y = the
+  // escape nibble (rank - 7, or 15 for a byte outside the table) already at
+  // byte k.  Four look-ups OR into the packed codes, the
   // escape mask and the escape bytes of four scalars with no shifting or
   // repacking afterwards.
   __align__(16) uint2 classes[4][256];
@@ -228,16 +229,20 @@ __device__ __forceinline__ uint32_t table_slot(uint32_t high) {
   return ((high << 1) | (high >> 7)) & 0xffu;
 }
 
-// Fills the class tables from `rank_of` and the selector table (one entry of
-// each per thread).
-__device__ __forceinline__ void load_classes(EncodeShared& sh, const uint8_t* rank_of, int tid) {
-  const uint32_t r = rank_of[tid];
+// Class-table entries of high byte `tid`, whose rank in the table is `r`.
+__device__ __forceinline__ void store_classes(EncodeShared& sh, uint32_t r, int tid) {
   const uint32_t code = min(r, (uint32_t)kPrimaryDirect);
   const uint32_t nib = r < kPrimaryDirect ? 0u : (r < kTableEntries ? r - kPrimaryDirect : 15u);
 #pragma unroll
   for (int k = 0; k < 4; ++k)
     sh.classes[k][table_slot((uint32_t)tid)] =
-        make_uint2((code << (4 * k)) | ((uint32_t)(r >= kPrimaryDirect) << (16 + k)), nib << (8 * k));
+        make_uint2((code << (4 * k)) | ((uint32_t)(r >= kPrimaryDirect) << (16 + k)) |
+                       ((uint32_t)(r >= kTableEntries) << (24 + k)),
+                   nib << (8 * k));
+}
+
+// Selector-table entry of escape mask `tid`.
+__device__ __forceinline__ void store_selectors(EncodeShared& sh, int tid) {
   uint32_t pick = 0x88888888u;
   int n = 0;
   for (int pos = 0; pos < 8; ++pos)
@@ -246,6 +251,13 @@ __device__ __forceinline__ void load_classes(EncodeShared& sh, const uint8_t* ra
       ++n;
     }
   sh.compact[tid] = pick;
+}
+
+// Fills the class tables from `rank_of` and the selector table (one entry of
+// each per thread).
+__device__ __forceinline__ void load_classes(EncodeShared& sh, const uint8_t* rank_of, int tid) {
+  store_classes(sh, rank_of[tid], tid);
+  store_selectors(sh, tid);
 }
 
 struct EncodePlan {
@@ -267,75 +279,98 @@ __device__ __forceinline__ uint2 classes4(const EncodeShared& sh, uint32_t hi, c
                     add_fma(add_fma(c0.y, c1.y, k), add_fma(c2.y, c3.y, k), k));
 }
 
-// `place(plan, raw)` is called by all lanes of warp 0 together and returns, in
-// every lane, where the record goes; it sets `raw` when the record must be
-// stored raw (it does not code, or it codes but no longer fits its page); a
-// null destination drops the record.
-//
-// `wd` is only read while the scalars are classified (the low bytes are set
-// aside in packed form as each word is consumed, so the 32 registers of the
-// record do not stay live to the end); the rare paths that need the original
-// words again - more escapes than the queue holds, a raw store - fetch them
-// with `reload(st)`.
-template <typename Reload, typename Place>
-__device__ __forceinline__ void encode_cta(const uint4 (&wd)[8], EncodeShared& sh, int tid,
-                                           const PipeConsts& k, Reload&& reload, Place&& place) {
-  const int lane = tid & 31, warp = tid >> 5;
-  for (int i = tid; i < kVarCap / 16; i += kOwners)
-    reinterpret_cast<uint4*>(sh.var)[i] = make_uint4(0, 0, 0, 0);
+// What classification leaves in an owner's registers.
+struct OwnerCodes {
+  uint32_t low[16];   // low bytes, packed in store order
+  uint32_t sym[6];    // symbol words
+  uint64_t queue;     // first 16 escape nibbles
+  uint32_t raw_q[4];  // first raw entries: local ordinal | high << 16
+  int n_esc, n_raw;
+};
 
-  // Classify the 64 scalars four at a time: primary codes as nibble words,
-  // escape nibbles appended to a queue (first 16; longer runs are redone below).
-  uint32_t codes[8], low[16];
-  uint64_t queue = 0;
-  uint32_t raw_q[4] = {0, 0, 0, 0};  // first raw entries: local ordinal | high << 16
-  int n_esc = 0, n_raw = 0;
+// Classifies the 64 scalars of an owner four at a time: primary codes as
+// nibble words, escape nibbles appended to a queue (the first 16; longer runs
+// are redone by build_variable_region).  `wd` is dead afterwards: the low bytes
+// are set aside in packed form as each word is consumed, so the 32 registers of
+// the record do not stay live to the end.  Scalars outside the table (raw
+// entries) are only marked while the words go by; their entries are made in
+// one short loop at the end, which fetches their high bytes with `reload(st)`
+// (word st of the owner's record): a warp that meets such scalars in most of
+// its words then diverges once, not once per word.
+template <typename Reload>
+__device__ __forceinline__ void classify(const uint4 (&wd)[8], const EncodeShared& sh,
+                                         const PipeConsts& k, OwnerCodes& o, Reload&& reload) {
+  uint32_t codes[8], marks[4];
+  o.queue = 0;
+  int n_esc = 0;
 #pragma unroll
   for (int st = 0; st < 8; ++st) {
     const uint32_t hi_a = __byte_perm(wd[st].x, wd[st].y, 0x7531);
     const uint32_t hi_b = __byte_perm(wd[st].z, wd[st].w, 0x7531);
-    low[2 * st] = __byte_perm(wd[st].x, wd[st].y, 0x6420);
-    low[2 * st + 1] = __byte_perm(wd[st].z, wd[st].w, 0x6420);
+    o.low[2 * st] = __byte_perm(wd[st].x, wd[st].y, 0x6420);
+    o.low[2 * st + 1] = __byte_perm(wd[st].z, wd[st].w, 0x6420);
     const uint2 ca = classes4(sh, hi_a, k), cb = classes4(sh, hi_b, k);
     codes[st] = prmt(ca.x, cb.x, 0x5410u);
+    // Byte 0: which of the eight scalars escape; byte 1: which are outside the table.
+    const uint32_t flags = (ca.x >> 16) | ((cb.x >> 16) << 4);
+    if (st & 1)
+      marks[st >> 1] = prmt(marks[st >> 1], flags, 0x5410u);
+    else
+      marks[st >> 1] = flags;
     // This word's escape nibbles, in order, without a loop over them (lanes
     // differ in how many they have; a loop runs as long as the worst lane).
-    const uint32_t mask8 = (ca.x >> 16) | ((cb.x >> 12) & 0xf0u);
+    const uint32_t mask8 = flags & 0xffu;
     const uint32_t pick = sh.compact[mask8];  // byte selectors that move flagged bytes to the front
     const uint32_t front_lo = prmt(ca.y, cb.y, pick), front_hi = prmt(ca.y, cb.y, pick >> 16);
-    const int here = __popc(mask8);
     // Eight bytes holding one nibble each -> eight adjacent nibbles: OR-ing a
     // word with itself shifted by four pairs the nibbles up in bytes 0 and 2.
     const uint32_t pair_lo = front_lo | (front_lo >> 4), pair_hi = front_hi | (front_hi >> 4);
     const uint32_t packed = prmt(pair_lo, pair_hi, 0x6420u);
-    if (n_esc < 16) queue |= (uint64_t)packed << (4 * n_esc);
-    // Raw scalars (nibble 15) are rare.
-    uint32_t raws = packed & (packed >> 1);
-    raws &= (raws >> 2) & 0x11111111u;
-    if (raws) {
-      const uint32_t high_lo = __byte_perm(hi_a, hi_b, pick), high_hi = __byte_perm(hi_a, hi_b, pick >> 16);
-      do {
-        const int at = (__ffs(raws) - 1) >> 2;
-        raws &= raws - 1;
-        const uint32_t high = ((at < 4 ? high_lo : high_hi) >> (8 * (at & 3))) & 0xffu;
-        const uint32_t entry = (uint32_t)(n_esc + at) | (high << 16);
-#pragma unroll
-        for (int x = 0; x < 4; ++x)
-          if (n_raw == x) raw_q[x] = entry;
-        ++n_raw;
-      } while (raws);
-    }
-    n_esc += here;
+    if (n_esc < 16) o.queue |= (uint64_t)packed << (4 * n_esc);
+    n_esc += __popc(mask8);
   }
-  // Symbol words: per 32-scalar group three words; bit 3 of word k's nibble j
-  // is bit k of the code of scalar 24 + j (attn_page.py:174-181).
-  uint32_t sym[6];
+  // Bit 8 st + e of esc / raw: scalar e of word st escapes / is outside the table.
+  const uint32_t esc[2] = {prmt(marks[0], marks[1], 0x6420u), prmt(marks[2], marks[3], 0x6420u)};
+  uint32_t raw[2] = {prmt(marks[0], marks[1], 0x7531u), prmt(marks[2], marks[3], 0x7531u)};
+  const int n_raw = __popc(raw[0]) + __popc(raw[1]);
+#pragma unroll
+  for (int x = 0; x < 4; ++x) {
+    o.raw_q[x] = 0;
+    if (x < n_raw && n_raw <= 4) {
+      const int half = raw[0] ? 0 : 1;
+      const uint32_t m = raw[half];
+      const int bit = __ffs(m) - 1;
+      raw[half] = m & (m - 1);
+      const uint32_t below = (1u << bit) - 1u;
+      const int ordinal = half ? __popc(esc[0]) + __popc(esc[1] & below) : __popc(esc[0] & below);
+      const uint4 w = reload(4 * half + (bit >> 3));
+      const int e = bit & 7;
+      const uint32_t pair = e < 4 ? (e < 2 ? w.x : w.y) : (e < 6 ? w.z : w.w);
+      const uint32_t high = (pair >> (8 + 16 * (e & 1))) & 0xffu;
+      o.raw_q[x] = (uint32_t)ordinal | (high << 16);
+    }
+  }
+  o.n_esc = n_esc;
+  o.n_raw = n_raw;
+  // Symbol words: per 32-scalar group three words; bit 3 of word b's nibble j
+  // is bit b of the code of scalar 24 + j (attn_page.py:174-181).
 #pragma unroll
   for (int gi = 0; gi < 2; ++gi)
 #pragma unroll
-    for (int k = 0; k < 3; ++k)
-      sym[3 * gi + k] = codes[4 * gi + k] | (((codes[4 * gi + 3] >> k) & 0x11111111u) << 3);
+    for (int b = 0; b < 3; ++b)
+      o.sym[3 * gi + b] = codes[4 * gi + b] | (((codes[4 * gi + 3] >> b) & 0x11111111u) << 3);
+}
 
+// Where an owner's escapes and raw entries go, and the record's plan.
+struct OwnerLayout {
+  int esc_at, raw_at, esc_total, raw_total, raw_offset;
+  EncodePlan plan;
+};
+
+// Ordinals of the owner's escapes and raw entries within the record (two warp
+// scans and one pass over the warps' sums; one barrier).
+__device__ __forceinline__ OwnerLayout record_layout(EncodeShared& sh, int n_esc, int n_raw, int tid) {
+  const int lane = tid & 31, warp = tid >> 5;
   const int esc_before = warp_exclusive_sum(n_esc, lane);
   const int raw_before = warp_exclusive_sum(n_raw, lane);
   if (lane == 31) {
@@ -343,57 +378,57 @@ __device__ __forceinline__ void encode_cta(const uint4 (&wd)[8], EncodeShared& s
     sh.warp_sum[1][warp] = raw_before + n_raw;
   }
   __syncthreads();
-  int esc_at = esc_before, raw_at = raw_before, esc_total = 0, raw_total = 0, raw_worst = 0;
+  OwnerLayout at;
+  at.esc_at = esc_before;
+  at.raw_at = raw_before;
+  at.esc_total = at.raw_total = 0;
+  int raw_worst = 0;
 #pragma unroll
   for (int w = 0; w < 8; ++w) {
     const int ew = sh.warp_sum[0][w], rw = sh.warp_sum[1][w];
     if (w < warp) {
-      esc_at += ew;
-      raw_at += rw;
+      at.esc_at += ew;
+      at.raw_at += rw;
     }
-    esc_total += ew;
-    raw_total += rw;
+    at.esc_total += ew;
+    at.raw_total += rw;
     raw_worst = max(raw_worst, rw);
   }
-  const int raw_offset = (kHeaderBytes + ((esc_total + 1) >> 1) + 3) & ~3;
-  EncodePlan plan;
-  plan.var_len = (raw_offset + 4 * raw_total + 15) & ~15;
-  plan.codes = plan.var_len <= kVarCap && raw_worst <= kMaxWarpRaw;
-  // Warp 0 places the record (global atomics, several microseconds) while the
-  // other warps build the variable region in shared memory; the destination is
-  // only needed for the final stores.
-  if (warp == 0) {
-    bool raw = !plan.codes;
-    uint8_t* dst = place(plan, raw);
-    if (lane == 0) {
-      sh.dst = dst;
-      sh.raw = raw;
-    }
-  }
+  at.raw_offset = (kHeaderBytes + ((at.esc_total + 1) >> 1) + 3) & ~3;
+  at.plan.var_len = (at.raw_offset + 4 * at.raw_total + 15) & ~15;
+  at.plan.codes = at.plan.var_len <= kVarCap && raw_worst <= kMaxWarpRaw;
+  return at;
+}
+
+// Builds the variable region in `sh.var` (zero beforehand, with a barrier in
+// between).  `reload(st)` fetches word st of the owner's record again for the
+// rare owner with more escapes or raw scalars than the queues hold.
+template <typename Reload>
+__device__ __forceinline__ void build_variable_region(EncodeShared& sh, const OwnerCodes& o,
+                                                      const OwnerLayout& at, int tid,
+                                                      Reload&& reload) {
+  if (!at.plan.codes) return;  // the record is stored raw
   uint32_t* var32 = reinterpret_cast<uint32_t*>(sh.var);
-  if (!plan.codes) {
-    // nothing to build: the record is stored raw
-  } else if (n_esc > 0 && n_esc <= 16) {
+  if (o.n_esc > 0 && o.n_esc <= 16) {
     // This owner's nibbles are consecutive from nibble `esc_at` of the stream
     // that starts at byte 48 (word 12).
-    const int word = (kHeaderBytes >> 2) + (esc_at >> 3), shift = 4 * (esc_at & 7);
-    const uint64_t lo = queue << shift;
-    const uint32_t hi = shift ? (uint32_t)(queue >> (64 - shift)) : 0u;
+    const int word = (kHeaderBytes >> 2) + (at.esc_at >> 3), shift = 4 * (at.esc_at & 7);
+    const uint64_t lo = o.queue << shift;
+    const uint32_t hi = shift ? (uint32_t)(o.queue >> (64 - shift)) : 0u;
     if ((uint32_t)lo) atomicOr(&var32[word], (uint32_t)lo);
     if ((uint32_t)(lo >> 32)) atomicOr(&var32[word + 1], (uint32_t)(lo >> 32));
     if (hi) atomicOr(&var32[word + 2], hi);
   }
-  if (plan.codes && n_raw > 0 && n_raw <= 4 && n_esc <= 16) {
+  if (o.n_raw > 0 && o.n_raw <= 4 && o.n_esc <= 16) {
     // Raw entries `ordinal | high << 16` (attn_page.py:188-191) from the queue.
 #pragma unroll
     for (int x = 0; x < 4; ++x)
-      if (x < n_raw) var32[(raw_offset >> 2) + raw_at + x] = raw_q[x] + (uint32_t)esc_at;
+      if (x < o.n_raw) var32[(at.raw_offset >> 2) + at.raw_at + x] = o.raw_q[x] + (uint32_t)at.esc_at;
   }
-  if (plan.codes && (n_esc > 16 || n_raw > 4)) {
-    // Rare: more escapes or raw scalars than the queues hold.  Walk the
-    // scalars again.
-    int ordinal = esc_at;
-#pragma unroll
+  if (o.n_esc > 16 || o.n_raw > 4) {
+    // Rare: walk the scalars again.
+    int ordinal = at.esc_at, raw_at = at.raw_at;
+#pragma unroll 1
     for (int st = 0; st < 8; ++st) {
       const uint4 w = reload(st);
       const uint32_t highs[2] = {__byte_perm(w.x, w.y, 0x7531), __byte_perm(w.z, w.w, 0x7531)};
@@ -403,20 +438,20 @@ __device__ __forceinline__ void encode_cta(const uint4 (&wd)[8], EncodeShared& s
         const uint2 c = sh.classes[0][table_slot(high)];
         if ((c.x & 0xfu) == (uint32_t)kPrimaryDirect) {
           const uint32_t nib = c.y;
-          if (n_esc > 16) {
+          if (o.n_esc > 16) {
             const int bit = 8 * kHeaderBytes + 4 * ordinal;
             atomicOr(&var32[bit >> 5], nib << (bit & 31));
           }
-          if (nib == 15u) var32[(raw_offset >> 2) + raw_at++] = (uint32_t)ordinal | (high << 16);
+          if (nib == 15u) var32[(at.raw_offset >> 2) + raw_at++] = (uint32_t)ordinal | (high << 16);
           ++ordinal;
         }
       }
     }
   }
   if (tid == 0) {
-    var32[0] = esc_total;
-    var32[1] = raw_total;
-    var32[2] = raw_offset;
+    var32[0] = at.esc_total;
+    var32[1] = at.raw_total;
+    var32[2] = at.raw_offset;
     var32[3] = 0;
     uint16_t* h16 = reinterpret_cast<uint16_t*>(sh.var);
     int e = 0, r = 0;
@@ -427,6 +462,39 @@ __device__ __forceinline__ void encode_cta(const uint4 (&wd)[8], EncodeShared& s
       r += sh.warp_sum[1][w];
     }
   }
+}
+
+// Dense part of a coded record: low bytes in four 16-byte chunks, symbols in
+// three 8-byte chunks, both chunk-major (attn_page.py:272-276).
+__device__ __forceinline__ void store_dense(uint8_t* dst, const uint4 (&low)[4], const uint2 (&sym)[3],
+                                            int tid) {
+#pragma unroll
+  for (int j = 0; j < 4; ++j) reinterpret_cast<uint4*>(dst)[j * kOwners + tid] = low[j];
+#pragma unroll
+  for (int m = 0; m < 3; ++m) reinterpret_cast<uint2*>(dst + kLowBytes)[m * kOwners + tid] = sym[m];
+}
+
+// One record on one CTA of 256 owners, start to end.  `place(plan, raw)` is
+// called by all lanes of warp 0 together and returns, in every lane, where the
+// record goes; it sets `raw` when the record must be stored raw; a null
+// destination drops the record.
+template <typename Reload, typename Place>
+__device__ __forceinline__ void encode_cta(const uint4 (&wd)[8], EncodeShared& sh, int tid,
+                                           const PipeConsts& k, Reload&& reload, Place&& place) {
+  for (int i = tid; i < kVarCap / 16; i += kOwners)
+    reinterpret_cast<uint4*>(sh.var)[i] = make_uint4(0, 0, 0, 0);
+  OwnerCodes o;
+  classify(wd, sh, k, o, reload);
+  const OwnerLayout at = record_layout(sh, o.n_esc, o.n_raw, tid);
+  if (tid < 32) {
+    bool raw = !at.plan.codes;
+    uint8_t* dst = place(at.plan, raw);
+    if (tid == 0) {
+      sh.dst = dst;
+      sh.raw = raw;
+    }
+  }
+  build_variable_region(sh, o, at, tid, reload);
   __syncthreads();  // placement known, variable region complete
   uint8_t* dst = sh.dst;
   if (dst == nullptr) return;
@@ -435,17 +503,14 @@ __device__ __forceinline__ void encode_cta(const uint4 (&wd)[8], EncodeShared& s
     for (int st = 0; st < 8; ++st) reinterpret_cast<uint4*>(dst)[st * kOwners + tid] = reload(st);
     return;
   }
-  // Dense part: low bytes in four 16-byte chunks, symbols in three 8-byte
-  // chunks, both chunk-major (attn_page.py:272-276).
-#pragma unroll
-  for (int j = 0; j < 4; ++j)
-    reinterpret_cast<uint4*>(dst)[j * kOwners + tid] =
-        make_uint4(low[4 * j], low[4 * j + 1], low[4 * j + 2], low[4 * j + 3]);
-#pragma unroll
-  for (int m = 0; m < 3; ++m)
-    reinterpret_cast<uint2*>(dst + kLowBytes)[m * kOwners + tid] =
-        make_uint2(sym[2 * m], sym[2 * m + 1]);
-  for (int i = tid; i < plan.var_len / 16; i += kOwners)
+  const uint4 low[4] = {make_uint4(o.low[0], o.low[1], o.low[2], o.low[3]),
+                        make_uint4(o.low[4], o.low[5], o.low[6], o.low[7]),
+                        make_uint4(o.low[8], o.low[9], o.low[10], o.low[11]),
+                        make_uint4(o.low[12], o.low[13], o.low[14], o.low[15])};
+  const uint2 sym[3] = {make_uint2(o.sym[0], o.sym[1]), make_uint2(o.sym[2], o.sym[3]),
+                        make_uint2(o.sym[4], o.sym[5])};
+  store_dense(dst, low, sym, tid);
+  for (int i = tid; i < at.plan.var_len / 16; i += kOwners)
     reinterpret_cast<uint4*>(dst + kDenseBytes)[i] = reinterpret_cast<const uint4*>(sh.var)[i];
 }
 
@@ -459,15 +524,24 @@ encode_kernel(StoreView v, int layer, uint8_t* arena, int64_t page_bytes, const 
               PipeConsts k) {
   __shared__ EncodeShared sh;
   const fp_store& s = v.s;
-  if ((int)blockIdx.x >= s.counters[FP_CTR_CLOSES]) return;
   const int rec = blockIdx.y, tid = threadIdx.x;
-  const int block = s.close_list[blockIdx.x];
-  uint8_t* src = v.staging(s.wslot[block], layer, rec);
-  const int64_t idx = v.table_index(layer, block, rec);
-  load_classes(sh, rank_of + ((int64_t)layer * 2 * s.H + rec) * 256, tid);
+  // counters -> close_list -> wslot -> record would be four dependent round
+  // trips before the first scalar can be classified.  The first two are
+  // independent loads, and the record is fetched before the count is checked
+  // (a stale list entry is clamped into range, so the fetch is always legal).
+  const int closes = s.counters[FP_CTR_CLOSES];
+  const int listed = s.close_list[blockIdx.x];
+  const uint32_t rank = rank_of[((int64_t)layer * 2 * s.H + rec) * 256 + tid];
+  const int block = min(max(listed, 0), s.NB - 1);
+  const int slot = min(max(s.wslot[block], 0), s.S_p + s.S_t - 1);
+  uint8_t* src = v.staging(slot, layer, rec);
   uint4 wd[8];
 #pragma unroll
   for (int st = 0; st < 8; ++st) wd[st] = reinterpret_cast<const uint4*>(src)[st * kOwners + tid];
+  if ((int)blockIdx.x >= closes) return;
+  const int64_t idx = v.table_index(layer, block, rec);
+  store_classes(sh, rank, tid);
+  store_selectors(sh, tid);
   __syncthreads();
   const auto reload = [&](int st) { return reinterpret_cast<const uint4*>(src)[st * kOwners + tid]; };
   encode_cta(wd, sh, tid, k, reload, [&](const EncodePlan& plan, bool& raw) -> uint8_t* {
