@@ -409,8 +409,15 @@ def run_decode(args, env: Env, name: str, arms: list[str], clocks: ClockSampler 
     if cfg.kv_heads % world:
         raise SystemExit(f"{world} GPUs do not divide {cfg.kv_heads} KV heads")
     per = cfg.kv_heads // world
-    head_slice = slice(rank * per, (rank + 1) * per)
     notes = []
+    if world == 1 and args.shard_of > 1:
+        # One GPU runs what one rank of an N-way KV-head split would (no gather).
+        if cfg.kv_heads % args.shard_of:
+            raise SystemExit(f"{args.shard_of} shards do not divide {cfg.kv_heads} KV heads")
+        per = cfg.kv_heads // args.shard_of
+        cfg = replace(cfg, name=f"{cfg.name}-shard-of-{args.shard_of}")
+        notes.append(f"one rank's shard of a {args.shard_of}-way KV-head split, without the gather")
+    head_slice = slice(rank * per, (rank + 1) * per)
     ref_mod = None
     arms = list(arms)
     if "reference" in arms:
@@ -1163,6 +1170,8 @@ def main() -> None:
     parser.add_argument("--seed", type=int, default=0)
     parser.add_argument("--batch", type=int, default=0, help="override the batch (profiling)")
     parser.add_argument("--ctx", type=int, default=0, help="override the context (profiling)")
+    parser.add_argument("--shard-of", type=int, default=0,
+                        help="one GPU: measure one rank's head shard of an N-way split (profiling)")
     parser.add_argument("--no-graph", action="store_true")
     parser.add_argument("--no-extras", action="store_true", help="headline workload only")
     parser.add_argument("--skip-validation", action="store_true",

@@ -25,10 +25,18 @@
 // rose.  P is rounded to BF16 and the denominator sums the unrounded
 // values, as in decode attention.
 //
-// This first version runs its phases one after another (decode K, S product,
-// decode V beside it, softmax, O product); every wait is bounded and reports
-// through the status word.  Nothing here uses thread-block clusters or
-// multicast.
+// The CTA is specialised by warp, and the phases of successive pages overlap:
+//   warps 0-7   decode records (the decoder's 256 owners): K of page p + 1 as
+//               soon as the S products of page p have read the K tile, V of page
+//               p + 1 as soon as the O products of page p have read the V tile;
+//   warps 8-11  softmax of query tile 0, warps 12-15 of query tile 1 (a warp
+//               reaches the tensor-memory lanes 32 (warp % 4) ..), running while
+//               the next page's K record is decoded;
+//   warp 16     one lane issues every tcgen05.mma: O_t(p) and then S_t(p + 1) as
+//               soon as tile t's probabilities of page p are written.
+// They meet only through mbarriers (K / V tile written, K / V tile read, S_t
+// ready, O_t done, P_t written); every wait is bounded and reports through the
+// status word.  Nothing here uses thread-block clusters or multicast.
 #include <math.h>
 
 #include "fp_api.h"
@@ -38,7 +46,9 @@
 namespace fpb {
 namespace {
 
-constexpr int kPrefillThreads = 256;  // eight warps decode; each warpgroup runs one tile's softmax
+constexpr int kDecoderThreads = 256;  // warps 0-7: the record decoder's owners
+constexpr int kSoftmaxThreads = 256;  // warps 8-15: one warpgroup per query tile, thread = row
+constexpr int kPrefillThreads = kDecoderThreads + kSoftmaxThreads + 32;  // + the warp that issues the products
 constexpr int kTile = 128;
 constexpr int kQTiles = 2;                     // query tiles per CTA, one per warpgroup
 constexpr int kTileBytes = kTile * kTile * 2;  // 32 KB: one operand tile
@@ -51,8 +61,12 @@ struct PrefillSmem {
   __align__(1024) uint8_t v[kTileBytes];
   __align__(1024) uint8_t p[kQTiles][kTileBytes];
   __align__(16) uint8_t esc[kEscBytes];
-  __align__(8) uint64_t bar_s;  // S product complete
-  __align__(8) uint64_t bar_o;  // O product complete
+  // Phase p of every barrier belongs to page p.
+  __align__(8) uint64_t k_ready, v_ready;      // decoders (256 arrivals): tile written
+  uint64_t k_free, v_free;                     // products that read the tile are complete
+  uint64_t s_ready[kQTiles], o_done[kQTiles];  // tile t's S / O products are complete
+  uint64_t p_ready[kQTiles];                   // tile t's softmax threads (128 arrivals): P written, S read
+  uint64_t drained;                            // every product issued by this CTA is complete
   uint32_t tmem_base;
   WaitState wait;
 };
@@ -73,6 +87,7 @@ struct PrefillParams {
   float scale_log2;
   PipeConsts k;
   long long wait_limit;
+  int skip_page;  // test hook: the decoders do not report this page's K tile (-1: none)
 };
 
 // Byte offset of the 16-byte chunk holding (row, col .. col + 7) of a K-major
@@ -189,6 +204,204 @@ __device__ __forceinline__ void record_to_tile(const uint8_t* rec, int vlen, con
     coded_record_words<true>(rec, vlen, tab, esc, tid, k, [] {}, emit);
 }
 
+// What every role needs to know about the CTA's work.
+struct PrefillWork {
+  int req, head, q0, n_q, ctx, first_pos, cta_tok0, rows_tokens;
+  int tile_last[kQTiles];  // last page query tile t needs; -1: the tile has no queries
+  int last_page;
+};
+
+// Decoder warps: K and V record of every page into the operand tiles.
+__device__ __forceinline__ void prefill_decode(const PrefillParams& p, PrefillSmem& sm,
+                                               const PrefillWork& w, int tid) {
+  const HeadTables tab_k = load_tables(p.plut, p.slut, w.head);
+  const HeadTables tab_v = load_tables(p.plut, p.slut, p.kvh + w.head);
+  const int32_t* bt = p.block_table + (int64_t)w.req * p.bt_stride;
+  const auto ask_l2 = [&](int page) {
+    // The records are decoded straight from global memory: thread 0 asks the L2
+    // for a later page's K record, thread 1 for its V record.
+    const int64_t at = (int64_t)bt[page] * 2 * p.kvh + w.head + tid * p.kvh;
+    const int32_t n = p.rec_len[at];
+    prefetch_l2(reinterpret_cast<const void*>(p.rec_addr[at]),
+                n > kVarCap || n < kHeaderBytes ? (uint32_t)kRawRecord
+                                                : (uint32_t)(kDenseBytes + (n & ~15)));
+  };
+  if (tid < 2 && w.last_page >= 1) ask_l2(1);
+  for (int page = 0; page <= w.last_page; ++page) {
+    const uint32_t before = (uint32_t)(page - 1) & 1u;
+    const int64_t idx = (int64_t)bt[page] * 2 * p.kvh + w.head;
+    if (tid < 2 && page + 2 <= w.last_page) ask_l2(page + 2);
+    // K tile: its readers are the S products of the page before.
+    if (page > 0) bounded_wait(&sm.k_free, before, &sm.wait);
+    record_to_tile(reinterpret_cast<const uint8_t*>(p.rec_addr[idx]), p.rec_len[idx], tab_k, sm.k,
+                   sm.esc, tid, p.k, kTile);
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    if (page != p.skip_page) mbar_arrive(&sm.k_ready);
+    // The escape scratch is shared by the two records: all owners are done with it.
+    asm volatile("bar.sync 1, %0;" ::"n"(kDecoderThreads) : "memory");
+    // V tile: its readers are the O products of the page before.  Columns
+    // (tokens) past the end of an open block are cleared.
+    if (page > 0) bounded_wait(&sm.v_free, before, &sm.wait);
+    record_to_tile(reinterpret_cast<const uint8_t*>(p.rec_addr[idx + p.kvh]),
+                   p.rec_len[idx + p.kvh], tab_v, sm.v, sm.esc, tid, p.k, w.ctx - page * kTile);
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    mbar_arrive(&sm.v_ready);
+    asm volatile("bar.sync 1, %0;" ::"n"(kDecoderThreads) : "memory");
+  }
+}
+
+// The thread that issues the products.  Order: S_t(0); then per page p and
+// tile t: O_t(p), S_t(p + 1) - the tensor pipe runs them in this order, so the
+// next page's scores are not held up behind the other tile's O product for
+// longer than one product.
+__device__ __forceinline__ void prefill_issue(PrefillSmem& sm, const PrefillWork& w, uint32_t tmem) {
+  const uint32_t q_addr[kQTiles] = {smem_addr(sm.q[0]), smem_addr(sm.q[1])};
+  const uint32_t p_addr[kQTiles] = {smem_addr(sm.p[0]), smem_addr(sm.p[1])};
+  const uint32_t k_addr = smem_addr(sm.k), v_addr = smem_addr(sm.v);
+  const auto last_tile = [&](int page) { return page <= w.tile_last[kQTiles - 1] ? kQTiles - 1 : 0; };
+  bounded_wait(&sm.k_ready, 0u, &sm.wait);
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll
+  for (int t = 0; t < kQTiles; ++t)
+    if (0 <= w.tile_last[t]) {
+      tile_product(tmem + (uint32_t)(t * kTile), q_addr[t], k_addr, false);
+      umma_commit(&sm.s_ready[t]);
+    }
+  umma_commit(&sm.k_free);
+  for (int page = 0; page <= w.last_page; ++page) {
+    const uint32_t parity = (uint32_t)page & 1u;
+    bool v_seen = false, k_seen = false;
+#pragma unroll
+    for (int t = 0; t < kQTiles; ++t) {
+      if (page <= w.tile_last[t]) {
+        bounded_wait(&sm.p_ready[t], parity, &sm.wait);
+        if (!v_seen) bounded_wait(&sm.v_ready, parity, &sm.wait);
+        v_seen = true;
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        tile_product(tmem + (uint32_t)((kQTiles + t) * kTile), p_addr[t], v_addr, page > 0);
+        umma_commit(&sm.o_done[t]);
+        if (t == last_tile(page)) umma_commit(&sm.v_free);
+      }
+      if (page + 1 <= w.tile_last[t]) {
+        if (!k_seen) bounded_wait(&sm.k_ready, parity ^ 1u, &sm.wait);
+        k_seen = true;
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        tile_product(tmem + (uint32_t)(t * kTile), q_addr[t], k_addr, false);
+        umma_commit(&sm.s_ready[t]);
+        if (t == last_tile(page + 1)) umma_commit(&sm.k_free);
+      }
+    }
+  }
+  // Tensor memory is given back at the end of the kernel: nothing may still be
+  // running there, also when a wait above gave up and the roles ran ahead.
+  umma_commit(&sm.drained);
+#pragma unroll 1
+  for (int tries = 0; tries < (1 << 20); ++tries)
+    if (mbar_try(&sm.drained, 0u, 1000u)) break;
+}
+
+// Softmax warpgroup of query tile `mine`: thread = query row.
+__device__ __forceinline__ void prefill_softmax(const PrefillParams& p, PrefillSmem& sm,
+                                                const PrefillWork& w, uint32_t tmem, int mine,
+                                                int row, int warp) {
+  const int my_last = w.tile_last[mine];
+  if (my_last < 0) return;
+  const int tok0 = w.cta_tok0 + mine * w.rows_tokens;
+  // Key positions <= row_pos are visible (rows past the request's queries
+  // compute like its last token and are not stored).
+  const int row_pos = min(w.first_pos + tok0 + row / p.group, w.ctx - 1);
+  float row_max = -INFINITY, row_sum = 0.f;
+  const uint32_t lane_base = (uint32_t)(32 * (warp & 3)) << 16;  // this warp's tensor-memory lanes
+  const uint32_t tmem_s = tmem + (uint32_t)(mine * kTile);
+  const uint32_t tmem_o = tmem + (uint32_t)((kQTiles + mine) * kTile);
+  uint8_t* p_tile = sm.p[mine];
+  uint32_t s[32];
+  for (int page = 0; page <= my_last; ++page) {
+    const uint32_t parity = (uint32_t)page & 1u;
+    bounded_wait(&sm.s_ready[mine], parity, &sm.wait);
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const int visible = row_pos - page * kTile;  // columns 0..visible of this page count
+    float page_max = -INFINITY;
+#pragma unroll 1
+    for (int c0 = 0; c0 < kTile; c0 += 32) {
+      tmem_load32(tmem_s + lane_base + (uint32_t)c0, s);
+#pragma unroll
+      for (int x = 0; x < 32; ++x)
+        if (c0 + x <= visible) page_max = fmaxf(page_max, __uint_as_float(s[x]) * p.scale_log2);
+    }
+    const float new_max = fmaxf(row_max, page_max);
+    // A row that sees no key yet keeps -inf; use 0 as its reference point.
+    const float ref = new_max == -INFINITY ? 0.f : new_max;
+    const float keep = ex2(row_max - ref);  // 0 while row_max is still -inf
+    // The O product of the page before reads the P tile and writes O.
+    if (page > 0) {
+      bounded_wait(&sm.o_done[mine], parity ^ 1u, &sm.wait);
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      // O rows are rescaled in tensor memory when some row of the warp's 32 rose.
+      if (__any_sync(0xffffffffu, new_max > row_max)) {
+#pragma unroll 1
+        for (int c0 = 0; c0 < kTile; c0 += 32) {
+          tmem_load32(tmem_o + lane_base + (uint32_t)c0, s);
+#pragma unroll
+          for (int x = 0; x < 32; ++x) s[x] = __float_as_uint(__uint_as_float(s[x]) * keep);
+          tmem_store32(tmem_o + lane_base + (uint32_t)c0, s);
+        }
+      }
+    }
+    row_sum *= keep;
+    row_max = new_max;
+#pragma unroll 1
+    for (int c0 = 0; c0 < kTile; c0 += 32) {
+      tmem_load32(tmem_s + lane_base + (uint32_t)c0, s);
+      uint32_t packed[16];
+#pragma unroll
+      for (int x = 0; x < 32; x += 2) {
+        const float a = c0 + x <= visible ? ex2(__uint_as_float(s[x]) * p.scale_log2 - ref) : 0.f;
+        const float b =
+            c0 + x + 1 <= visible ? ex2(__uint_as_float(s[x + 1]) * p.scale_log2 - ref) : 0.f;
+        row_sum += a + b;
+        const __nv_bfloat162 pair = __floats2bfloat162_rn(a, b);
+        packed[x >> 1] = *reinterpret_cast<const uint32_t*>(&pair);
+      }
+#pragma unroll
+      for (int ch = 0; ch < 4; ++ch)
+        *reinterpret_cast<uint4*>(p_tile + tile_chunk(row, c0 + 8 * ch)) =
+            make_uint4(packed[4 * ch], packed[4 * ch + 1], packed[4 * ch + 2], packed[4 * ch + 3]);
+    }
+    // P written, S read, O rescaled: the issuing thread may go on.
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    mbar_arrive(&sm.p_ready[mine]);
+  }
+
+  // ---- epilogue: O / row_sum -> BF16 rows of `out`.
+  bounded_wait(&sm.o_done[mine], (uint32_t)my_last & 1u, &sm.wait);
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const int tok = tok0 + row / p.group, g = row % p.group;
+  const float inv = row_sum > 0.f ? 1.f / row_sum : 0.f;
+  __nv_bfloat16* dst =
+      p.out + (int64_t)(w.q0 + tok) * p.out_stride + (int64_t)(w.head * p.group + g) * 128;
+#pragma unroll 1
+  for (int c0 = 0; c0 < kTile; c0 += 32) {
+    tmem_load32(tmem_o + lane_base + (uint32_t)c0, s);
+    if (tok < w.n_q) {
+#pragma unroll
+      for (int ch = 0; ch < 4; ++ch) {
+        uint32_t o[4];
+#pragma unroll
+        for (int x = 0; x < 4; ++x) {
+          const __nv_bfloat162 pair =
+              __floats2bfloat162_rn(__uint_as_float(s[8 * ch + 2 * x]) * inv,
+                                    __uint_as_float(s[8 * ch + 2 * x + 1]) * inv);
+          o[x] = *reinterpret_cast<const uint32_t*>(&pair);
+        }
+        *reinterpret_cast<uint4*>(dst + c0 + 8 * ch) = make_uint4(o[0], o[1], o[2], o[3]);
+      }
+    }
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+}
+
 __global__ void __launch_bounds__(kPrefillThreads, 1) prefill_attn_kernel(PrefillParams p) {
   // The operand tiles must start on 1024-byte boundaries (the swizzle is a
   // function of the address); the launch reserves the slack for this.
@@ -196,26 +409,35 @@ __global__ void __launch_bounds__(kPrefillThreads, 1) prefill_attn_kernel(Prefil
   PrefillSmem& sm =
       *reinterpret_cast<PrefillSmem*>(dyn + ((1024u - (smem_addr(dyn) & 1023u)) & 1023u));
   const int tid = threadIdx.x, warp = tid >> 5;
-  const int req = blockIdx.z, head = blockIdx.y;
-  const int rows_tokens = kTile / p.group;  // query tokens per tile
-  const int q0 = p.q_start[req], n_q = p.q_start[req + 1] - q0;
-  const int cta_tok0 = blockIdx.x * kQTiles * rows_tokens;
-  if (cta_tok0 >= n_q) return;  // uniform over the CTA, before anything is allocated
-  const int ctx = p.ctx_len[req];
-  const int first_pos = ctx - n_q;  // position of the request's first query token
-  // Last page each query tile needs (-1: the tile lies past the request's
-  // queries); the CTA walks the pages of its last tile.
-  int tile_last[kQTiles];
+  PrefillWork w;
+  w.req = blockIdx.z;
+  w.head = blockIdx.y;
+  w.rows_tokens = kTile / p.group;  // query tokens per tile
+  w.q0 = p.q_start[w.req];
+  w.n_q = p.q_start[w.req + 1] - w.q0;
+  w.cta_tok0 = blockIdx.x * kQTiles * w.rows_tokens;
+  if (w.cta_tok0 >= w.n_q) return;  // uniform over the CTA, before anything is allocated
+  w.ctx = p.ctx_len[w.req];
+  w.first_pos = w.ctx - w.n_q;  // position of the request's first query token
 #pragma unroll
   for (int t = 0; t < kQTiles; ++t) {
-    const int t0 = cta_tok0 + t * rows_tokens;
-    tile_last[t] = t0 < n_q ? (first_pos + min(t0 + rows_tokens, n_q) - 1) >> 7 : -1;
+    const int t0 = w.cta_tok0 + t * w.rows_tokens;
+    w.tile_last[t] = t0 < w.n_q ? (w.first_pos + min(t0 + w.rows_tokens, w.n_q) - 1) >> 7 : -1;
   }
-  const int last_page = max(tile_last[0], tile_last[kQTiles - 1]);
+  w.last_page = max(w.tile_last[0], w.tile_last[kQTiles - 1]);
 
   if (tid == 0) {
-    mbar_init(&sm.bar_s, 1);
-    mbar_init(&sm.bar_o, 1);
+    mbar_init(&sm.k_ready, kDecoderThreads);
+    mbar_init(&sm.v_ready, kDecoderThreads);
+    mbar_init(&sm.k_free, 1);
+    mbar_init(&sm.v_free, 1);
+    mbar_init(&sm.drained, 1);
+#pragma unroll
+    for (int t = 0; t < kQTiles; ++t) {
+      mbar_init(&sm.s_ready[t], 1);
+      mbar_init(&sm.o_done[t], 1);
+      mbar_init(&sm.p_ready[t], kSoftmaxThreads / kQTiles);
+    }
     sm.wait.abort = 0;
     sm.wait.status = p.status;
     sm.wait.limit = p.wait_limit;
@@ -232,11 +454,11 @@ __global__ void __launch_bounds__(kPrefillThreads, 1) prefill_attn_kernel(Prefil
   // Q tiles: row = token * G + head of the group, zero rows past the request's queries.
   for (int x = tid; x < kQTiles * kTile * 16; x += kPrefillThreads) {
     const int t = x / (kTile * 16), row = (x >> 4) & (kTile - 1), col = (x & 15) * 8;
-    const int tok = cta_tok0 + t * rows_tokens + row / p.group, g = row % p.group;
+    const int tok = w.cta_tok0 + t * w.rows_tokens + row / p.group, g = row % p.group;
     uint4 val = make_uint4(0u, 0u, 0u, 0u);
-    if (tok < n_q)
-      val = *reinterpret_cast<const uint4*>(p.q + (int64_t)(q0 + tok) * p.q_stride +
-                                            (int64_t)(head * p.group + g) * 128 + col);
+    if (tok < w.n_q)
+      val = *reinterpret_cast<const uint4*>(p.q + (int64_t)(w.q0 + tok) * p.q_stride +
+                                            (int64_t)(w.head * p.group + g) * 128 + col);
     *reinterpret_cast<uint4*>(sm.q[t] + tile_chunk(row, col)) = val;
   }
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -244,148 +466,16 @@ __global__ void __launch_bounds__(kPrefillThreads, 1) prefill_attn_kernel(Prefil
   __syncthreads();
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const uint32_t tmem = sm.tmem_base;
-  const HeadTables tab_k = load_tables(p.plut, p.slut, head);
-  const HeadTables tab_v = load_tables(p.plut, p.slut, p.kvh + head);
-  const int32_t* bt = p.block_table + (int64_t)req * p.bt_stride;
 
-  // Softmax state of this thread's query row: warpgroup `mine` owns query tile
-  // `mine`, thread = row.  Key positions <= row_pos are visible (rows past the
-  // request's queries compute like its last token and are not stored).
-  const int mine = warp >> 2, row = tid & (kTile - 1);
-  const int tok0 = cta_tok0 + mine * rows_tokens;
-  const int my_last = mine == 0 ? tile_last[0] : tile_last[kQTiles - 1];
-  const int row_pos = min(first_pos + tok0 + row / p.group, ctx - 1);
-  float row_max = -INFINITY, row_sum = 0.f;
-  const uint32_t lane_base = (uint32_t)(32 * (warp & 3)) << 16;  // this warp's tensor-memory lanes
-  const uint32_t tmem_s = tmem + (uint32_t)(mine * kTile);
-  const uint32_t tmem_o = tmem + (uint32_t)((kQTiles + mine) * kTile);
-  uint8_t* p_tile = sm.p[mine];
-
-  for (int page = 0; page <= last_page; ++page) {
-    const uint32_t parity = (uint32_t)page & 1u;
-    const int64_t idx = (int64_t)bt[page] * 2 * p.kvh + head;
-    const int open_cols = ctx - page * kTile;  // tokens of this block that exist
-    if (tid < 2 && page < last_page) {
-      // The records are decoded straight from global memory: ask the L2 for the
-      // next page's K (thread 0) and V (thread 1) record while this page is worked on.
-      const int64_t next = (int64_t)bt[page + 1] * 2 * p.kvh + head + tid * p.kvh;
-      const int32_t n = p.rec_len[next];
-      prefetch_l2(reinterpret_cast<const void*>(p.rec_addr[next]),
-                  n > kVarCap || n < kHeaderBytes ? (uint32_t)kRawRecord
-                                                  : (uint32_t)(kDenseBytes + (n & ~15)));
-    }
-    // ---- K record -> K tile (its previous readers, the S products of the page
-    // before, finished before that page's softmax began).
-    record_to_tile(reinterpret_cast<const uint8_t*>(p.rec_addr[idx]), p.rec_len[idx], tab_k, sm.k,
-                   sm.esc, tid, p.k, kTile);
-    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-    __syncthreads();
-    if (tid == 0) {
-      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-#pragma unroll
-      for (int t = 0; t < kQTiles; ++t)
-        if (page <= tile_last[t])
-          tile_product(tmem + (uint32_t)(t * kTile), smem_addr(sm.q[t]), smem_addr(sm.k), false);
-      umma_commit(&sm.bar_s);
-    }
-    // ---- V record -> V tile while the S products run; the O products of the
-    // page before must be done with the V and P tiles (and with O) first.
-    if (page > 0) bounded_wait(&sm.bar_o, parity ^ 1u, &sm.wait);
-    record_to_tile(reinterpret_cast<const uint8_t*>(p.rec_addr[idx + p.kvh]),
-                   p.rec_len[idx + p.kvh], tab_v, sm.v, sm.esc, tid, p.k, open_cols);
-    // ---- softmax: one thread per query row of the warpgroup's tile (a tile
-    // whose queries all lie before this page has nothing to add).
-    if (page <= my_last) {
-      bounded_wait(&sm.bar_s, parity, &sm.wait);
-      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      const int visible = row_pos - page * kTile;  // columns 0..visible of this page count
-      float page_max = -INFINITY;
-      uint32_t s[32];
-#pragma unroll 1
-      for (int c0 = 0; c0 < kTile; c0 += 32) {
-        tmem_load32(tmem_s + lane_base + (uint32_t)c0, s);
-#pragma unroll
-        for (int x = 0; x < 32; ++x)
-          if (c0 + x <= visible) page_max = fmaxf(page_max, __uint_as_float(s[x]) * p.scale_log2);
-      }
-      const float new_max = fmaxf(row_max, page_max);
-      // A row that sees no key yet keeps -inf; use 0 as its reference point.
-      const float ref = new_max == -INFINITY ? 0.f : new_max;
-      const float keep = ex2(row_max - ref);  // 0 while row_max is still -inf
-      // O rows are rescaled in tensor memory when some row of the warp's 32 rose.
-      if (page > 0 && __any_sync(0xffffffffu, new_max > row_max)) {
-#pragma unroll 1
-        for (int c0 = 0; c0 < kTile; c0 += 32) {
-          tmem_load32(tmem_o + lane_base + (uint32_t)c0, s);
-#pragma unroll
-          for (int x = 0; x < 32; ++x) s[x] = __float_as_uint(__uint_as_float(s[x]) * keep);
-          tmem_store32(tmem_o + lane_base + (uint32_t)c0, s);
-        }
-      }
-      row_sum *= keep;
-      row_max = new_max;
-#pragma unroll 1
-      for (int c0 = 0; c0 < kTile; c0 += 32) {
-        tmem_load32(tmem_s + lane_base + (uint32_t)c0, s);
-        uint32_t packed[16];
-#pragma unroll
-        for (int x = 0; x < 32; x += 2) {
-          const float a = c0 + x <= visible ? ex2(__uint_as_float(s[x]) * p.scale_log2 - ref) : 0.f;
-          const float b =
-              c0 + x + 1 <= visible ? ex2(__uint_as_float(s[x + 1]) * p.scale_log2 - ref) : 0.f;
-          row_sum += a + b;
-          const __nv_bfloat162 pair = __floats2bfloat162_rn(a, b);
-          packed[x >> 1] = *reinterpret_cast<const uint32_t*>(&pair);
-        }
-#pragma unroll
-        for (int ch = 0; ch < 4; ++ch)
-          *reinterpret_cast<uint4*>(p_tile + tile_chunk(row, c0 + 8 * ch)) =
-              make_uint4(packed[4 * ch], packed[4 * ch + 1], packed[4 * ch + 2], packed[4 * ch + 3]);
-      }
-      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-    }
-    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-    __syncthreads();  // V and P tiles complete, S read, O rescaled
-    if (tid == 0) {
-      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-#pragma unroll
-      for (int t = 0; t < kQTiles; ++t)
-        if (page <= tile_last[t])
-          tile_product(tmem + (uint32_t)((kQTiles + t) * kTile), smem_addr(sm.p[t]), smem_addr(sm.v),
-                       page > 0);
-      umma_commit(&sm.bar_o);
-    }
+  if (tid < kDecoderThreads) {
+    prefill_decode(p, sm, w, tid);
+  } else if (tid < kDecoderThreads + kSoftmaxThreads) {
+    const int row = (tid - kDecoderThreads) & (kTile - 1);
+    prefill_softmax(p, sm, w, tmem, (tid - kDecoderThreads) / kTile, row, warp);
+  } else if (tid == kDecoderThreads + kSoftmaxThreads) {
+    prefill_issue(sm, w, tmem);
   }
-
-  // ---- epilogue: O / row_sum -> BF16 rows of `out`.
-  if (my_last >= 0) {
-    bounded_wait(&sm.bar_o, (uint32_t)last_page & 1u, &sm.wait);
-    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    const int tok = tok0 + row / p.group, g = row % p.group;
-    const float inv = row_sum > 0.f ? 1.f / row_sum : 0.f;
-    __nv_bfloat16* dst =
-        p.out + (int64_t)(q0 + tok) * p.out_stride + (int64_t)(head * p.group + g) * 128;
-    uint32_t o[32];
-#pragma unroll 1
-    for (int c0 = 0; c0 < kTile; c0 += 32) {
-      tmem_load32(tmem_o + lane_base + (uint32_t)c0, o);
-      if (tok < n_q) {
-#pragma unroll
-        for (int ch = 0; ch < 4; ++ch) {
-          uint32_t w[4];
-#pragma unroll
-          for (int x = 0; x < 4; ++x) {
-            const __nv_bfloat162 pair =
-                __floats2bfloat162_rn(__uint_as_float(o[8 * ch + 2 * x]) * inv,
-                                      __uint_as_float(o[8 * ch + 2 * x + 1]) * inv);
-            w[x] = *reinterpret_cast<const uint32_t*>(&pair);
-          }
-          *reinterpret_cast<uint4*>(dst + c0 + 8 * ch) = make_uint4(w[0], w[1], w[2], w[3]);
-        }
-      }
-    }
-    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
   if (warp == 0) {
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -444,6 +534,7 @@ int fp_prefill_attention(const void* q, int64_t q_stride, const int64_t* rec_add
   p.scale_log2 = scale * 1.4426950408889634f;
   p.k = pipe_consts();
   p.wait_limit = wait_debug().limit;
+  p.skip_page = (int)std::max<long long>(-1, std::min<long long>(wait_debug().skip_record, 1 << 20));
   const int cta_tokens = kQTiles * (kTile / group);  // query tokens per CTA
   const dim3 grid((unsigned)((max_query_tokens + cta_tokens - 1) / cta_tokens), (unsigned)kv_heads,
                   (unsigned)num_requests);
