@@ -12,17 +12,18 @@
 // cores (tcgen05.mma, accumulators in tensor memory), per query tile:
 //
 //   S = Q K^T      A = Q tile [128 rows, 128 dims], B = K tile [128 tokens, 128 dims]
-//   O += P V       A = P tile [128 rows, 128 tokens], B = V tile [128 dims, 128 tokens]
+//   O += P V       A = P [128 rows, 128 tokens] in tensor memory, B = V tile [128 dims, 128 tokens]
 //
-// All four tiles are K-major with the 128-byte swizzle (eight 16-byte chunks
+// The three shared-memory tiles are K-major with the 128-byte swizzle (eight 16-byte chunks
 // of a row XOR-ed with the row index modulo 8), which is also what stmatrix
 // can write from the record decoder's mma fragments: a K record yields rows =
 // tokens, a V record rows = dims, with the same store.  The two S tiles live in
 // tensor memory columns 0..255, the two O tiles in columns 256..511; each
 // warpgroup (four warps) owns one query tile and reads its S with tcgen05.ld,
-// one thread per query row (no shuffles in the softmax), writes P as BF16 into
-// its operand tile, and rescales its O in tensor memory when a row's maximum
-// rose.  P is rounded to BF16 and the denominator sums the unrounded
+// one thread per query row (no shuffles in the softmax), writes P as BF16 over
+// the first half of its S columns (two values per 32-bit cell: the A operand of
+// the O product is read from tensor memory), and rescales its O in tensor
+// memory when a row's maximum rose.  P is rounded to BF16 and the denominator sums the unrounded
 // values, as in decode attention.
 //
 // The CTA is specialised by warp, and the phases of successive pages overlap:
@@ -33,9 +34,13 @@
 //               reaches the tensor-memory lanes 32 (warp % 4) ..), running while
 //               the next page's K record is decoded;
 //   warp 16     one lane issues every tcgen05.mma: O_t(p) and then S_t(p + 1) as
-//               soon as tile t's probabilities of page p are written.
-// They meet only through mbarriers (K / V tile written, K / V tile read, S_t
-// ready, O_t done, P_t written); every wait is bounded and reports through the
+//               soon as tile t's probabilities of page p are written (in this
+//               order, so that S_t(p + 1) overwrites P_t(p) after it was used);
+//   warp 17     streams the coded records into a three-slot ring of shared
+//               memory with bulk copies, 32 table look-ups at a time (raw
+//               records, the open tails, are read in place).
+// They meet only through mbarriers (ring slot full / empty, K / V tile written,
+// K / V tile read, S_t ready, O_t done, P_t written); every wait is bounded and reports through the
 // status word.  Nothing here uses thread-block clusters or multicast.
 #include <math.h>
 
@@ -48,7 +53,10 @@ namespace {
 
 constexpr int kDecoderThreads = 256;  // warps 0-7: the record decoder's owners
 constexpr int kSoftmaxThreads = 256;  // warps 8-15: one warpgroup per query tile, thread = row
-constexpr int kPrefillThreads = kDecoderThreads + kSoftmaxThreads + 32;  // + the warp that issues the products
+constexpr int kIssuerThread = kDecoderThreads + kSoftmaxThreads;  // lane 0 of warp 16
+constexpr int kProducerWarp = 17;
+constexpr int kPrefillThreads = kDecoderThreads + kSoftmaxThreads + 64;
+constexpr int kRingSlots = 3;
 constexpr int kTile = 128;
 constexpr int kQTiles = 2;                     // query tiles per CTA, one per warpgroup
 constexpr int kTileBytes = kTile * kTile * 2;  // 32 KB: one operand tile
@@ -59,14 +67,17 @@ struct PrefillSmem {
   __align__(1024) uint8_t q[kQTiles][kTileBytes];
   __align__(1024) uint8_t k[kTileBytes];
   __align__(1024) uint8_t v[kTileBytes];
-  __align__(1024) uint8_t p[kQTiles][kTileBytes];
+  __align__(128) uint8_t ring[kRingSlots][kCodedMax];  // coded records, as stored
   __align__(16) uint8_t esc[kEscBytes];
+  int64_t addr[kRingSlots];  // where the slot's record lives (raw records are read there)
+  int32_t vlen[kRingSlots];
   // Phase p of every barrier belongs to page p.
   __align__(8) uint64_t k_ready, v_ready;      // decoders (256 arrivals): tile written
   uint64_t k_free, v_free;                     // products that read the tile are complete
   uint64_t s_ready[kQTiles], o_done[kQTiles];  // tile t's S / O products are complete
   uint64_t p_ready[kQTiles];                   // tile t's softmax threads (128 arrivals): P written, S read
   uint64_t drained;                            // every product issued by this CTA is complete
+  uint64_t full[kRingSlots], empty[kRingSlots];  // ring: copy landed / the decoders' 8 warps are done
   uint32_t tmem_base;
   WaitState wait;
 };
@@ -117,6 +128,17 @@ __device__ __forceinline__ void umma(uint32_t d_tmem, uint64_t a_desc, uint64_t 
       : "memory");
 }
 
+// The same with the A operand in tensor memory: 128 rows on the 128 lanes, two
+// BF16 values per 32-bit column, so a K = 16 step spans eight columns.
+__device__ __forceinline__ void umma_tmem_a(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc,
+                                            bool accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(kInstrDesc), "r"((uint32_t)accumulate)
+      : "memory");
+}
+
 // D (+)= A B over the tiles' 128-deep contraction: eight K = 16 steps, each
 // 32 bytes further along the row (four per swizzle atom column).
 __device__ __forceinline__ void tile_product(uint32_t d_tmem, uint32_t a_addr, uint32_t b_addr,
@@ -125,6 +147,15 @@ __device__ __forceinline__ void tile_product(uint32_t d_tmem, uint32_t a_addr, u
   for (int j = 0; j < 8; ++j) {
     const uint32_t step = (uint32_t)((j >> 2) * kHalfTile + (j & 3) * 32);
     umma(d_tmem, tile_desc(a_addr + step), tile_desc(b_addr + step), accumulate || j > 0);
+  }
+}
+
+__device__ __forceinline__ void tile_product_tmem_a(uint32_t d_tmem, uint32_t a_tmem, uint32_t b_addr,
+                                                    bool accumulate) {
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    const uint32_t step = (uint32_t)((j >> 2) * kHalfTile + (j & 3) * 32);
+    umma_tmem_a(d_tmem, a_tmem + 8u * (uint32_t)j, tile_desc(b_addr + step), accumulate || j > 0);
   }
 }
 
@@ -163,6 +194,17 @@ __device__ __forceinline__ void tmem_store32(uint32_t taddr, const uint32_t (&r)
       : "memory");
 }
 
+__device__ __forceinline__ void tmem_store16(uint32_t taddr, const uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};\n\t"
+      "tcgen05.wait::st.sync.aligned;"
+      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]),
+        "r"(r[7]), "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]),
+        "r"(r[15])
+      : "memory");
+}
+
 __device__ __forceinline__ float ex2(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
@@ -176,10 +218,14 @@ __device__ __forceinline__ float ex2(float x) {
 // the fragment's row, so one stmatrix per word stores all four pieces; lane
 // 8 m + r supplies the address of row r of piece m = 2 j + f.  `valid_cols`
 // clears the columns (tokens of a V record) past the end of an open block, so
-// that stale bytes there cannot meet a zero probability as NaN.
-__device__ __forceinline__ void record_to_tile(const uint8_t* rec, int vlen, const HeadTables& tab,
-                                               uint8_t* tile, uint8_t* esc, int tid,
-                                               const PipeConsts& k, int valid_cols) {
+// that stale bytes there cannot meet a zero probability as NaN.  A coded
+// record is read from its ring slot `staged`, a raw one in place; `released`
+// is called once the slot is no longer needed.
+template <typename Released>
+__device__ __forceinline__ void record_to_tile(const uint8_t* staged, int64_t in_place, int vlen,
+                                               const HeadTables& tab, uint8_t* tile, uint8_t* esc,
+                                               int tid, const PipeConsts& k, int valid_cols,
+                                               Released&& released) {
   const int lane = tid & 31, warp = tid >> 5;
   const int r = lane & 7, j = (lane >> 4) & 1, f = (lane >> 3) & 1, c = lane & 3;
   const uint32_t base = smem_addr(tile);
@@ -198,10 +244,12 @@ __device__ __forceinline__ void record_to_tile(const uint8_t* rec, int vlen, con
                  "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3])
                  : "memory");
   };
-  if (vlen > kVarCap || vlen < kHeaderBytes)
-    raw_record_words(rec, tid, emit);
-  else
-    coded_record_words<true>(rec, vlen, tab, esc, tid, k, [] {}, emit);
+  if (vlen > kVarCap || vlen < kHeaderBytes) {
+    released();
+    raw_record_words(reinterpret_cast<const uint8_t*>(in_place), tid, emit);
+  } else {
+    coded_record_words(staged, vlen, tab, esc, tid, k, released, emit);
+  }
 }
 
 // What every role needs to know about the CTA's work.
@@ -211,42 +259,84 @@ struct PrefillWork {
   int last_page;
 };
 
-// Decoder warps: K and V record of every page into the operand tiles.
+// Producer warp: the records of the CTA's pages, K then V, into the ring.
+// Lane L resolves the L-th of the next 32 records (block table -> record
+// address and length), lane 0 then issues them in order.
+__device__ __forceinline__ void prefill_produce(const PrefillParams& p, PrefillSmem& sm,
+                                                const PrefillWork& w, int lane) {
+  const int32_t* bt = p.block_table + (int64_t)w.req * p.bt_stride;
+  const int records = 2 * (w.last_page + 1);
+  volatile int* abort = &sm.wait.abort;
+  for (int base = 0; base < records; base += 32) {
+    const int n = base + lane;
+    int64_t addr = 0;
+    int32_t vlen = 0;
+    if (n < records) {
+      const int64_t at = (int64_t)bt[n >> 1] * 2 * p.kvh + w.head + (n & 1) * p.kvh;
+      addr = p.rec_addr[at];
+      vlen = p.rec_len[at];
+    }
+    const int count = min(32, records - base);
+    for (int j = 0; j < count; ++j) {
+      const int64_t a = __shfl_sync(0xffffffffu, addr, j);
+      const int32_t v = __shfl_sync(0xffffffffu, vlen, j);
+      const uint32_t r = (uint32_t)(base + j), slot = r % kRingSlots, use = r / kRingSlots;
+      if (lane == 0) {
+        bool ok = true;
+        if (use > 0) ok = bounded_wait(&sm.empty[slot], (use - 1) & 1u, &sm.wait);
+        if (ok) {
+          sm.addr[slot] = a;
+          sm.vlen[slot] = v;
+          if (v > kVarCap || v < kHeaderBytes) {
+            prefetch_l2(reinterpret_cast<const void*>(a), kRawRecord);
+            mbar_arrive(&sm.full[slot]);
+          } else {
+            const uint32_t bytes = (uint32_t)(kDenseBytes + (v & ~15));
+            mbar_expect_tx(&sm.full[slot], bytes);
+            bulk_load(sm.ring[slot], reinterpret_cast<const void*>(a), bytes, &sm.full[slot]);
+          }
+        }
+      }
+      __syncwarp();
+      if (*abort) return;
+    }
+  }
+}
+
+// Decoder warps: K and V record of every page out of the ring into the operand tiles.
 __device__ __forceinline__ void prefill_decode(const PrefillParams& p, PrefillSmem& sm,
                                                const PrefillWork& w, int tid) {
   const HeadTables tab_k = load_tables(p.plut, p.slut, w.head);
   const HeadTables tab_v = load_tables(p.plut, p.slut, p.kvh + w.head);
-  const int32_t* bt = p.block_table + (int64_t)w.req * p.bt_stride;
-  const auto ask_l2 = [&](int page) {
-    // The records are decoded straight from global memory: thread 0 asks the L2
-    // for a later page's K record, thread 1 for its V record.
-    const int64_t at = (int64_t)bt[page] * 2 * p.kvh + w.head + tid * p.kvh;
-    const int32_t n = p.rec_len[at];
-    prefetch_l2(reinterpret_cast<const void*>(p.rec_addr[at]),
-                n > kVarCap || n < kHeaderBytes ? (uint32_t)kRawRecord
-                                                : (uint32_t)(kDenseBytes + (n & ~15)));
-  };
-  if (tid < 2 && w.last_page >= 1) ask_l2(1);
+  const int lane = tid & 31;
+  uint32_t r = 0;  // records taken from the ring so far
   for (int page = 0; page <= w.last_page; ++page) {
     const uint32_t before = (uint32_t)(page - 1) & 1u;
-    const int64_t idx = (int64_t)bt[page] * 2 * p.kvh + w.head;
-    if (tid < 2 && page + 2 <= w.last_page) ask_l2(page + 2);
-    // K tile: its readers are the S products of the page before.
-    if (page > 0) bounded_wait(&sm.k_free, before, &sm.wait);
-    record_to_tile(reinterpret_cast<const uint8_t*>(p.rec_addr[idx]), p.rec_len[idx], tab_k, sm.k,
-                   sm.esc, tid, p.k, kTile);
-    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-    if (page != p.skip_page) mbar_arrive(&sm.k_ready);
-    // The escape scratch is shared by the two records: all owners are done with it.
-    asm volatile("bar.sync 1, %0;" ::"n"(kDecoderThreads) : "memory");
-    // V tile: its readers are the O products of the page before.  Columns
-    // (tokens) past the end of an open block are cleared.
-    if (page > 0) bounded_wait(&sm.v_free, before, &sm.wait);
-    record_to_tile(reinterpret_cast<const uint8_t*>(p.rec_addr[idx + p.kvh]),
-                   p.rec_len[idx + p.kvh], tab_v, sm.v, sm.esc, tid, p.k, w.ctx - page * kTile);
-    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-    mbar_arrive(&sm.v_ready);
-    asm volatile("bar.sync 1, %0;" ::"n"(kDecoderThreads) : "memory");
+#pragma unroll
+    for (int kv = 0; kv < 2; ++kv, ++r) {
+      const uint32_t slot = r % kRingSlots;
+      // A record whose wait ran out is not decoded (the status word marks the call invalid).
+      const bool landed = bounded_wait(&sm.full[slot], (r / kRingSlots) & 1u, &sm.wait);
+      const auto released = [&] {
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&sm.empty[slot]);
+      };
+      // The tile's readers are the S (K tile) / O (V tile) products of the page before.
+      if (page > 0) bounded_wait(kv == 0 ? &sm.k_free : &sm.v_free, before, &sm.wait);
+      if (landed) {
+        // Columns (tokens) of a V tile past the end of an open block are cleared.
+        record_to_tile(sm.ring[slot], sm.addr[slot], sm.vlen[slot], kv == 0 ? tab_k : tab_v,
+                       kv == 0 ? sm.k : sm.v, sm.esc, tid, p.k,
+                       kv == 0 ? kTile : w.ctx - page * kTile, released);
+      }
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      if (kv == 1)
+        mbar_arrive(&sm.v_ready);
+      else if (page != p.skip_page)
+        mbar_arrive(&sm.k_ready);
+      // The escape scratch is shared by consecutive records: all owners are done with it.
+      asm volatile("bar.sync 1, %0;" ::"n"(kDecoderThreads) : "memory");
+    }
   }
 }
 
@@ -256,7 +346,6 @@ __device__ __forceinline__ void prefill_decode(const PrefillParams& p, PrefillSm
 // longer than one product.
 __device__ __forceinline__ void prefill_issue(PrefillSmem& sm, const PrefillWork& w, uint32_t tmem) {
   const uint32_t q_addr[kQTiles] = {smem_addr(sm.q[0]), smem_addr(sm.q[1])};
-  const uint32_t p_addr[kQTiles] = {smem_addr(sm.p[0]), smem_addr(sm.p[1])};
   const uint32_t k_addr = smem_addr(sm.k), v_addr = smem_addr(sm.v);
   const auto last_tile = [&](int page) { return page <= w.tile_last[kQTiles - 1] ? kQTiles - 1 : 0; };
   bounded_wait(&sm.k_ready, 0u, &sm.wait);
@@ -278,7 +367,9 @@ __device__ __forceinline__ void prefill_issue(PrefillSmem& sm, const PrefillWork
         if (!v_seen) bounded_wait(&sm.v_ready, parity, &sm.wait);
         v_seen = true;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        tile_product(tmem + (uint32_t)((kQTiles + t) * kTile), p_addr[t], v_addr, page > 0);
+        // P_t sits in the first half of S_t's columns.
+        tile_product_tmem_a(tmem + (uint32_t)((kQTiles + t) * kTile), tmem + (uint32_t)(t * kTile),
+                            v_addr, page > 0);
         umma_commit(&sm.o_done[t]);
         if (t == last_tile(page)) umma_commit(&sm.v_free);
       }
@@ -314,7 +405,6 @@ __device__ __forceinline__ void prefill_softmax(const PrefillParams& p, PrefillS
   const uint32_t lane_base = (uint32_t)(32 * (warp & 3)) << 16;  // this warp's tensor-memory lanes
   const uint32_t tmem_s = tmem + (uint32_t)(mine * kTile);
   const uint32_t tmem_o = tmem + (uint32_t)((kQTiles + mine) * kTile);
-  uint8_t* p_tile = sm.p[mine];
   uint32_t s[32];
   for (int page = 0; page <= my_last; ++page) {
     const uint32_t parity = (uint32_t)page & 1u;
@@ -333,7 +423,8 @@ __device__ __forceinline__ void prefill_softmax(const PrefillParams& p, PrefillS
     // A row that sees no key yet keeps -inf; use 0 as its reference point.
     const float ref = new_max == -INFINITY ? 0.f : new_max;
     const float keep = ex2(row_max - ref);  // 0 while row_max is still -inf
-    // The O product of the page before reads the P tile and writes O.
+    // The O product of the page before writes O (and read P, which the S
+    // product of this page has since overwritten).
     if (page > 0) {
       bounded_wait(&sm.o_done[mine], parity ^ 1u, &sm.wait);
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -363,13 +454,11 @@ __device__ __forceinline__ void prefill_softmax(const PrefillParams& p, PrefillS
         const __nv_bfloat162 pair = __floats2bfloat162_rn(a, b);
         packed[x >> 1] = *reinterpret_cast<const uint32_t*>(&pair);
       }
-#pragma unroll
-      for (int ch = 0; ch < 4; ++ch)
-        *reinterpret_cast<uint4*>(p_tile + tile_chunk(row, c0 + 8 * ch)) =
-            make_uint4(packed[4 * ch], packed[4 * ch + 1], packed[4 * ch + 2], packed[4 * ch + 3]);
+      // P over the S columns already read: chunk i of 32 scores becomes 16
+      // cells at columns 16 i .., always behind the read position.
+      tmem_store16(tmem_s + lane_base + (uint32_t)(c0 >> 1), packed);
     }
     // P written, S read, O rescaled: the issuing thread may go on.
-    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     mbar_arrive(&sm.p_ready[mine]);
   }
@@ -433,6 +522,11 @@ __global__ void __launch_bounds__(kPrefillThreads, 1) prefill_attn_kernel(Prefil
     mbar_init(&sm.v_free, 1);
     mbar_init(&sm.drained, 1);
 #pragma unroll
+    for (int i = 0; i < kRingSlots; ++i) {
+      mbar_init(&sm.full[i], 1);
+      mbar_init(&sm.empty[i], kDecoderThreads / 32);
+    }
+#pragma unroll
     for (int t = 0; t < kQTiles; ++t) {
       mbar_init(&sm.s_ready[t], 1);
       mbar_init(&sm.o_done[t], 1);
@@ -472,8 +566,10 @@ __global__ void __launch_bounds__(kPrefillThreads, 1) prefill_attn_kernel(Prefil
   } else if (tid < kDecoderThreads + kSoftmaxThreads) {
     const int row = (tid - kDecoderThreads) & (kTile - 1);
     prefill_softmax(p, sm, w, tmem, (tid - kDecoderThreads) / kTile, row, warp);
-  } else if (tid == kDecoderThreads + kSoftmaxThreads) {
+  } else if (tid == kIssuerThread) {
     prefill_issue(sm, w, tmem);
+  } else if (warp == kProducerWarp) {
+    prefill_produce(p, sm, w, tid & 31);
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
