@@ -27,16 +27,17 @@
 // values, as in decode attention.
 //
 // The CTA is specialised by warp, and the phases of successive pages overlap:
-//   warps 0-7   decode records (the decoder's 256 owners): K of page p + 1 as
-//               soon as the S products of page p have read the K tile, V of page
-//               p + 1 as soon as the O products of page p have read the V tile;
-//   warps 8-11  softmax of query tile 0, warps 12-15 of query tile 1 (a warp
+//   warps 0-7   decode K records (the decoder's 256 owners): K of page p + 1 as
+//               soon as the S products of page p have read the K tile;
+//   warps 8-15  decode V records, side by side with the K team: V of page p + 1
+//               as soon as the O products of page p have read the V tile;
+//   warps 16-19 softmax of query tile 0, warps 20-23 of query tile 1 (a warp
 //               reaches the tensor-memory lanes 32 (warp % 4) ..), running while
-//               the next page's K record is decoded;
-//   warp 16     one lane issues every tcgen05.mma: O_t(p) and then S_t(p + 1) as
+//               the next page's records are decoded;
+//   warp 24     one lane issues every tcgen05.mma: O_t(p) and then S_t(p + 1) as
 //               soon as tile t's probabilities of page p are written (in this
 //               order, so that S_t(p + 1) overwrites P_t(p) after it was used);
-//   warp 17     streams the coded records into a three-slot ring of shared
+//   warp 25     streams the coded records into the two teams' slots of shared
 //               memory with bulk copies, 32 table look-ups at a time (raw
 //               records, the open tails, are read in place).
 // They meet only through mbarriers (ring slot full / empty, K / V tile written,
@@ -51,12 +52,14 @@
 namespace fpb {
 namespace {
 
-constexpr int kDecoderThreads = 256;  // warps 0-7: the record decoder's owners
-constexpr int kSoftmaxThreads = 256;  // warps 8-15: one warpgroup per query tile, thread = row
-constexpr int kIssuerThread = kDecoderThreads + kSoftmaxThreads;  // lane 0 of warp 16
-constexpr int kProducerWarp = 17;
+constexpr int kTeamThreads = 256;  // one decoder team: the record decoder's 256 owners
+constexpr int kDecoderThreads = 2 * kTeamThreads;  // warps 0-7 decode K records, warps 8-15 V records
+constexpr int kSoftmaxThreads = 256;  // warps 16-23: one warpgroup per query tile, thread = row
+constexpr int kIssuerThread = kDecoderThreads + kSoftmaxThreads;  // lane 0 of warp 24
+constexpr int kProducerWarp = 25;
 constexpr int kPrefillThreads = kDecoderThreads + kSoftmaxThreads + 64;
-constexpr int kRingSlots = 3;
+constexpr int kRingSlots = 2;  // records alternate K, V: slot 0 serves the K team, slot 1 the V team
+constexpr float kRescaleSlack = 8.f;
 constexpr int kTile = 128;
 constexpr int kQTiles = 2;                     // query tiles per CTA, one per warpgroup
 constexpr int kTileBytes = kTile * kTile * 2;  // 32 KB: one operand tile
@@ -68,16 +71,16 @@ struct PrefillSmem {
   __align__(1024) uint8_t k[kTileBytes];
   __align__(1024) uint8_t v[kTileBytes];
   __align__(128) uint8_t ring[kRingSlots][kCodedMax];  // coded records, as stored
-  __align__(16) uint8_t esc[kEscBytes];
+  __align__(16) uint8_t esc[2][kEscBytes];  // escape scratch of the K team and of the V team
   int64_t addr[kRingSlots];  // where the slot's record lives (raw records are read there)
   int32_t vlen[kRingSlots];
   // Phase p of every barrier belongs to page p.
-  __align__(8) uint64_t k_ready, v_ready;      // decoders (256 arrivals): tile written
+  __align__(8) uint64_t k_ready, v_ready;      // decoder team (256 arrivals): tile written
   uint64_t k_free, v_free;                     // products that read the tile are complete
   uint64_t s_ready[kQTiles], o_done[kQTiles];  // tile t's S / O products are complete
   uint64_t p_ready[kQTiles];                   // tile t's softmax threads (128 arrivals): P written, S read
   uint64_t drained;                            // every product issued by this CTA is complete
-  uint64_t full[kRingSlots], empty[kRingSlots];  // ring: copy landed / the decoders' 8 warps are done
+  uint64_t full[kRingSlots], empty[kRingSlots];  // ring: copy landed / the team's 8 warps are done
   uint32_t tmem_base;
   WaitState wait;
 };
@@ -180,6 +183,28 @@ __device__ __forceinline__ void tmem_load32(uint32_t taddr, uint32_t (&r)[32]) {
       : "memory");
 }
 
+// The same load without the wait: the caller overlaps it with arithmetic on
+// an earlier chunk and calls tmem_wait_loads() before it reads `r`.
+__device__ __forceinline__ void tmem_load32_async(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+        "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
+        "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]),
+        "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
+        "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_wait_loads() {
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_wait_stores() {
+  asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+}
+
 __device__ __forceinline__ void tmem_store32(uint32_t taddr, const uint32_t (&r)[32]) {
   asm volatile(
       "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
@@ -194,11 +219,11 @@ __device__ __forceinline__ void tmem_store32(uint32_t taddr, const uint32_t (&r)
       : "memory");
 }
 
+// No wait inside: the caller calls tmem_wait_stores() once after its last store.
 __device__ __forceinline__ void tmem_store16(uint32_t taddr, const uint32_t (&r)[16]) {
   asm volatile(
       "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
-      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};\n\t"
-      "tcgen05.wait::st.sync.aligned;"
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
       ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]),
         "r"(r[7]), "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]),
         "r"(r[15])
@@ -303,40 +328,38 @@ __device__ __forceinline__ void prefill_produce(const PrefillParams& p, PrefillS
   }
 }
 
-// Decoder warps: K and V record of every page out of the ring into the operand tiles.
+// A decoder team (kv = 0: K records, 1: V records; `tid` within the team):
+// its record of every page out of its ring slot into its operand tile.  The two
+// teams run side by side, so a page costs one record's decode time, not two.
 __device__ __forceinline__ void prefill_decode(const PrefillParams& p, PrefillSmem& sm,
-                                               const PrefillWork& w, int tid) {
-  const HeadTables tab_k = load_tables(p.plut, p.slut, w.head);
-  const HeadTables tab_v = load_tables(p.plut, p.slut, p.kvh + w.head);
+                                               const PrefillWork& w, int kv, int tid) {
+  const HeadTables tab = load_tables(p.plut, p.slut, kv * p.kvh + w.head);
   const int lane = tid & 31;
-  uint32_t r = 0;  // records taken from the ring so far
+  uint64_t* const full = &sm.full[kv];
+  uint64_t* const tile_free = kv == 0 ? &sm.k_free : &sm.v_free;
+  uint64_t* const tile_ready = kv == 0 ? &sm.k_ready : &sm.v_ready;
+  uint8_t* const tile = kv == 0 ? sm.k : sm.v;
+  const auto released = [&] {
+    __syncwarp();
+    if (lane == 0) mbar_arrive(&sm.empty[kv]);
+  };
   for (int page = 0; page <= w.last_page; ++page) {
-    const uint32_t before = (uint32_t)(page - 1) & 1u;
-#pragma unroll
-    for (int kv = 0; kv < 2; ++kv, ++r) {
-      const uint32_t slot = r % kRingSlots;
-      // A record whose wait ran out is not decoded (the status word marks the call invalid).
-      const bool landed = bounded_wait(&sm.full[slot], (r / kRingSlots) & 1u, &sm.wait);
-      const auto released = [&] {
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&sm.empty[slot]);
-      };
-      // The tile's readers are the S (K tile) / O (V tile) products of the page before.
-      if (page > 0) bounded_wait(kv == 0 ? &sm.k_free : &sm.v_free, before, &sm.wait);
-      if (landed) {
-        // Columns (tokens) of a V tile past the end of an open block are cleared.
-        record_to_tile(sm.ring[slot], sm.addr[slot], sm.vlen[slot], kv == 0 ? tab_k : tab_v,
-                       kv == 0 ? sm.k : sm.v, sm.esc, tid, p.k,
-                       kv == 0 ? kTile : w.ctx - page * kTile, released);
-      }
-      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-      if (kv == 1)
-        mbar_arrive(&sm.v_ready);
-      else if (page != p.skip_page)
-        mbar_arrive(&sm.k_ready);
-      // The escape scratch is shared by consecutive records: all owners are done with it.
-      asm volatile("bar.sync 1, %0;" ::"n"(kDecoderThreads) : "memory");
+    // A record whose wait ran out is not decoded (the status word marks the call invalid).
+    const bool landed = bounded_wait(full, (uint32_t)page & 1u, &sm.wait);
+    // The tile's readers are the S (K tile) / O (V tile) products of the page before.
+    if (page > 0) bounded_wait(tile_free, (uint32_t)(page - 1) & 1u, &sm.wait);
+    if (landed) {
+      // Columns (tokens) of a V tile past the end of an open block are cleared.
+      record_to_tile(sm.ring[kv], sm.addr[kv], sm.vlen[kv], tab, tile, sm.esc[kv], tid, p.k,
+                     kv == 0 ? kTile : w.ctx - page * kTile, released);
     }
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    if (kv == 1 || page != p.skip_page) mbar_arrive(tile_ready);
+    // The team's escape scratch is reused by its next record: all owners are done with it.
+    if (kv == 0)
+      asm volatile("bar.sync 1, %0;" ::"n"(kTeamThreads) : "memory");
+    else
+      asm volatile("bar.sync 2, %0;" ::"n"(kTeamThreads) : "memory");
   }
 }
 
@@ -391,6 +414,40 @@ __device__ __forceinline__ void prefill_issue(PrefillSmem& sm, const PrefillWork
     if (mbar_try(&sm.drained, 0u, 1000u)) break;
 }
 
+// Largest of 32 raw scores, columns first .. first + 31 of the page; kMasked:
+// only the columns up to `visible` count.
+template <bool kMasked>
+__device__ __forceinline__ float chunk_max(const uint32_t (&s)[32], int first, int visible, float m) {
+#pragma unroll
+  for (int x = 0; x < 32; x += 2) {
+    float a = __uint_as_float(s[x]), b = __uint_as_float(s[x + 1]);
+    if (kMasked && first + x > visible) a = -INFINITY;
+    if (kMasked && first + x + 1 > visible) b = -INFINITY;
+    m = fmaxf(m, fmaxf(a, b));
+  }
+  return m;
+}
+
+// exp2(score * scale - ref) of 32 scores as 16 BF16 pairs; returns their sum
+// (of the unrounded values).
+template <bool kMasked>
+__device__ __forceinline__ float chunk_probabilities(const uint32_t (&s)[32], int first, int visible,
+                                                     float scale, float ref,
+                                                     uint32_t (&packed)[16]) {
+  float sum = 0.f;
+#pragma unroll
+  for (int x = 0; x < 32; x += 2) {
+    float a = ex2(fmaf(__uint_as_float(s[x]), scale, -ref));
+    float b = ex2(fmaf(__uint_as_float(s[x + 1]), scale, -ref));
+    if (kMasked && first + x > visible) a = 0.f;
+    if (kMasked && first + x + 1 > visible) b = 0.f;
+    sum += a + b;
+    const __nv_bfloat162 pair = __floats2bfloat162_rn(a, b);
+    packed[x >> 1] = *reinterpret_cast<const uint32_t*>(&pair);
+  }
+  return sum;
+}
+
 // Softmax warpgroup of query tile `mine`: thread = query row.
 __device__ __forceinline__ void prefill_softmax(const PrefillParams& p, PrefillSmem& sm,
                                                 const PrefillWork& w, uint32_t tmem, int mine,
@@ -405,31 +462,46 @@ __device__ __forceinline__ void prefill_softmax(const PrefillParams& p, PrefillS
   const uint32_t lane_base = (uint32_t)(32 * (warp & 3)) << 16;  // this warp's tensor-memory lanes
   const uint32_t tmem_s = tmem + (uint32_t)(mine * kTile);
   const uint32_t tmem_o = tmem + (uint32_t)((kQTiles + mine) * kTile);
-  uint32_t s[32];
+  uint32_t s[32], s2[32];
   for (int page = 0; page <= my_last; ++page) {
     const uint32_t parity = (uint32_t)page & 1u;
     bounded_wait(&sm.s_ready[mine], parity, &sm.wait);
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const int visible = row_pos - page * kTile;  // columns 0..visible of this page count
-    float page_max = -INFINITY;
-#pragma unroll 1
-    for (int c0 = 0; c0 < kTile; c0 += 32) {
-      tmem_load32(tmem_s + lane_base + (uint32_t)c0, s);
+    // Only the pages on the diagonal need the causal mask (uniform over the warp).
+    const bool masked = __any_sync(0xffffffffu, visible < kTile - 1);
+    // Two chunks of 32 scores in flight: the load of the next overlaps the
+    // arithmetic on this one.  The scale is positive, so the largest raw score
+    // gives the largest scaled one.
+    float raw_max = -INFINITY;
+    tmem_load32_async(tmem_s + lane_base, s);
+    tmem_wait_loads();
 #pragma unroll
-      for (int x = 0; x < 32; ++x)
-        if (c0 + x <= visible) page_max = fmaxf(page_max, __uint_as_float(s[x]) * p.scale_log2);
+    for (int c = 0; c < 4; ++c) {
+      uint32_t(&cur)[32] = (c & 1) ? s2 : s;
+      uint32_t(&nxt)[32] = (c & 1) ? s : s2;
+      if (c < 3) tmem_load32_async(tmem_s + lane_base + (uint32_t)(32 * (c + 1)), nxt);
+      raw_max = masked ? chunk_max<true>(cur, 32 * c, visible, raw_max)
+                       : chunk_max<false>(cur, 32 * c, visible, raw_max);
+      tmem_wait_loads();
     }
-    const float new_max = fmaxf(row_max, page_max);
+    const float page_max = raw_max * p.scale_log2;
+    // The reference point of the exponentials follows the running maximum only
+    // when that rose by more than kRescaleSlack (in log2 units): probabilities
+    // then stay below 2^kRescaleSlack, exact in FP32 and BF16 alike, and O is
+    // rescaled a few times per request instead of on almost every page (among
+    // 32 rows some maximum nearly always creeps up a little).
+    const bool rise = page_max > row_max + kRescaleSlack;  // row_max is -inf until a key is seen
+    const float new_max = rise ? page_max : row_max;
     // A row that sees no key yet keeps -inf; use 0 as its reference point.
     const float ref = new_max == -INFINITY ? 0.f : new_max;
-    const float keep = ex2(row_max - ref);  // 0 while row_max is still -inf
+    const float keep = rise ? ex2(row_max - ref) : 1.f;  // 0 while row_max is still -inf
     // The O product of the page before writes O (and read P, which the S
     // product of this page has since overwritten).
     if (page > 0) {
       bounded_wait(&sm.o_done[mine], parity ^ 1u, &sm.wait);
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      // O rows are rescaled in tensor memory when some row of the warp's 32 rose.
-      if (__any_sync(0xffffffffu, new_max > row_max)) {
+      if (__any_sync(0xffffffffu, rise)) {
 #pragma unroll 1
         for (int c0 = 0; c0 < kTile; c0 += 32) {
           tmem_load32(tmem_o + lane_base + (uint32_t)c0, s);
@@ -441,23 +513,22 @@ __device__ __forceinline__ void prefill_softmax(const PrefillParams& p, PrefillS
     }
     row_sum *= keep;
     row_max = new_max;
-#pragma unroll 1
-    for (int c0 = 0; c0 < kTile; c0 += 32) {
-      tmem_load32(tmem_s + lane_base + (uint32_t)c0, s);
-      uint32_t packed[16];
+    // P over the S columns already read: chunk c of 32 scores becomes 16 cells
+    // at columns 16 c .., always behind the read position.
+    tmem_load32_async(tmem_s + lane_base, s);
+    tmem_wait_loads();
 #pragma unroll
-      for (int x = 0; x < 32; x += 2) {
-        const float a = c0 + x <= visible ? ex2(__uint_as_float(s[x]) * p.scale_log2 - ref) : 0.f;
-        const float b =
-            c0 + x + 1 <= visible ? ex2(__uint_as_float(s[x + 1]) * p.scale_log2 - ref) : 0.f;
-        row_sum += a + b;
-        const __nv_bfloat162 pair = __floats2bfloat162_rn(a, b);
-        packed[x >> 1] = *reinterpret_cast<const uint32_t*>(&pair);
-      }
-      // P over the S columns already read: chunk i of 32 scores becomes 16
-      // cells at columns 16 i .., always behind the read position.
-      tmem_store16(tmem_s + lane_base + (uint32_t)(c0 >> 1), packed);
+    for (int c = 0; c < 4; ++c) {
+      uint32_t(&cur)[32] = (c & 1) ? s2 : s;
+      uint32_t(&nxt)[32] = (c & 1) ? s : s2;
+      if (c < 3) tmem_load32_async(tmem_s + lane_base + (uint32_t)(32 * (c + 1)), nxt);
+      uint32_t packed[16];
+      row_sum += masked ? chunk_probabilities<true>(cur, 32 * c, visible, p.scale_log2, ref, packed)
+                        : chunk_probabilities<false>(cur, 32 * c, visible, p.scale_log2, ref, packed);
+      tmem_wait_loads();
+      tmem_store16(tmem_s + lane_base + (uint32_t)(16 * c), packed);
     }
+    tmem_wait_stores();
     // P written, S read, O rescaled: the issuing thread may go on.
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     mbar_arrive(&sm.p_ready[mine]);
@@ -516,15 +587,15 @@ __global__ void __launch_bounds__(kPrefillThreads, 1) prefill_attn_kernel(Prefil
   w.last_page = max(w.tile_last[0], w.tile_last[kQTiles - 1]);
 
   if (tid == 0) {
-    mbar_init(&sm.k_ready, kDecoderThreads);
-    mbar_init(&sm.v_ready, kDecoderThreads);
+    mbar_init(&sm.k_ready, kTeamThreads);
+    mbar_init(&sm.v_ready, kTeamThreads);
     mbar_init(&sm.k_free, 1);
     mbar_init(&sm.v_free, 1);
     mbar_init(&sm.drained, 1);
 #pragma unroll
     for (int i = 0; i < kRingSlots; ++i) {
       mbar_init(&sm.full[i], 1);
-      mbar_init(&sm.empty[i], kDecoderThreads / 32);
+      mbar_init(&sm.empty[i], kTeamThreads / 32);
     }
 #pragma unroll
     for (int t = 0; t < kQTiles; ++t) {
@@ -562,7 +633,7 @@ __global__ void __launch_bounds__(kPrefillThreads, 1) prefill_attn_kernel(Prefil
   const uint32_t tmem = sm.tmem_base;
 
   if (tid < kDecoderThreads) {
-    prefill_decode(p, sm, w, tid);
+    prefill_decode(p, sm, w, tid / kTeamThreads, tid % kTeamThreads);
   } else if (tid < kDecoderThreads + kSoftmaxThreads) {
     const int row = (tid - kDecoderThreads) & (kTile - 1);
     prefill_softmax(p, sm, w, tmem, (tid - kDecoderThreads) / kTile, row, warp);
