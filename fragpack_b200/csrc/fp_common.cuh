@@ -156,7 +156,7 @@ __device__ __forceinline__ void raw_record_words(const uint8_t* rec, int tid, Em
 //
 // `rec` may be shared or global memory.  `esc` is a kEscBytes scratch in
 // shared memory.  `released()` is called after the last read of `rec` by this
-// warp.  Within one record each warp touches only its own part of `esc`,
+// warp: at the end, or with kEagerLow before the words are assembled.  Within one record each warp touches only its own part of `esc`,
 // so only warp-level synchronisation happens in here; but the parts move with
 // the record's escape prefixes, so two records may share one scratch only if a
 // block-wide barrier separates their decodes.
@@ -259,6 +259,13 @@ __device__ __forceinline__ void coded_record_words(const uint8_t* rec, int vlen,
         for (int j = 0; j < 4; ++j) mine[4 * (x - j) + j] = (uint8_t)(patch >> 16);
       }
     }
+  }
+
+  if (kEagerLow) {
+    // Symbols and low bytes are in registers, escapes in the scratch: the
+    // record itself is no longer needed.
+    __syncwarp();
+    released();
   }
 
   // Selector words (3-bit codes, bit 3 clear) of the eight words; escapes are
@@ -390,8 +397,10 @@ __device__ __forceinline__ void coded_record_words(const uint8_t* rec, int vlen,
                            __byte_perm(lb, hb, 0x5140), __byte_perm(lb, hb, 0x7362)};
     emit(st, w);
   }
-  __syncwarp();
-  released();
+  if (!kEagerLow) {
+    __syncwarp();
+    released();
+  }
 }
 
 // One owner's view of where its word scalars live in a token-major tile.

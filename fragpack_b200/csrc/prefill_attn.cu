@@ -273,7 +273,9 @@ __device__ __forceinline__ void record_to_tile(const uint8_t* staged, int64_t in
     released();
     raw_record_words(reinterpret_cast<const uint8_t*>(in_place), tid, emit);
   } else {
-    coded_record_words(staged, vlen, tab, esc, tid, k, released, emit);
+    // Low bytes up front, so that the slot is free for the next record's copy
+    // while this one is still being assembled.
+    coded_record_words<true>(staged, vlen, tab, esc, tid, k, released, emit);
   }
 }
 
