@@ -672,6 +672,7 @@ int fp_prefill_attention(const void* q, int64_t q_stride, const int64_t* rec_add
                  kv_heads <= 65535,
              "bad prefill geometry (%d requests, %d query tokens, %d KV heads)", num_requests,
              max_query_tokens, kv_heads);
+  FP_REQUIRE(scale > 0.f, "the softmax scale must be positive");
   FP_REQUIRE(group == 1 || group == 2 || group == 4 || group == 8,
              "query group %d must be 1, 2, 4 or 8", group);
   FP_REQUIRE(q && rec_addr && rec_len && plut && slut && block_table && q_start && ctx_len && out &&

@@ -240,6 +240,7 @@ int fp_fused_decode_noalloc(const void* q, int64_t q_stride, const int64_t* rec_
  *   ctx_len     int32 [R]: its context length, the new tokens included (they
  *               must already be in the store: fp_hbm_write comes first)
  *   max_query_tokens  the most query rows of any request (sizes the grid)
+ *   scale       softmax scale, > 0
  *   status      one int32 of the caller, zeroed once: the kernel ORs
  *               FP_DECODE_WAIT_TIMEOUT into it when a bounded wait ran out
  * Query i of request r sits at position ctx_len[r] - n_r + i and attends the
