@@ -152,16 +152,25 @@ write_kernel(StoreView v, const uint16_t* key, const uint16_t* value, int64_t ks
     if (!(tok_flags[k] & 2)) continue;
     const int w = tok_slot[k], group = tok_off[k] >> 4;
     const int64_t first = t0 + k;
-    for (int h = 0; h < heads; ++h) {
+    // All of the CTA's heads are fetched before the first is transposed: the
+    // loads of four heads (64 KB per CTA) are in flight together instead of one
+    // head's between two barriers.
+    const int row = tid >> 4, col = tid & 15;  // 16 tokens x 16 chunks of 16 bytes
+    uint4 kk[kWriteHeads], vv[kWriteHeads];
+#pragma unroll
+    for (int h = 0; h < kWriteHeads; ++h)
+      if (h < heads) {
+        const int head = head0 + h;
+        kk[h] = *reinterpret_cast<const uint4*>(key + (first + row) * ks0 + head * ks1 + 8 * col);
+        vv[h] = *reinterpret_cast<const uint4*>(value + (first + row) * vs0 + head * vs1 + 8 * col);
+      }
+#pragma unroll
+    for (int h = 0; h < kWriteHeads; ++h) {
+      if (h >= heads) break;
       const int head = head0 + h;
       __syncthreads();  // the previous tile has been read
-      {
-        const int row = tid >> 4, col = tid & 15;  // 16 tokens x 16 chunks of 16 bytes
-        const uint4 kk = *reinterpret_cast<const uint4*>(key + (first + row) * ks0 + head * ks1 + 8 * col);
-        const uint4 vv = *reinterpret_cast<const uint4*>(value + (first + row) * vs0 + head * vs1 + 8 * col);
-        *reinterpret_cast<uint4*>(&tile[0][row][16 * col]) = kk;
-        *reinterpret_cast<uint4*>(&tile[1][row][16 * col]) = vv;
-      }
+      *reinterpret_cast<uint4*>(&tile[0][row][16 * col]) = kk[h];
+      *reinterpret_cast<uint4*>(&tile[1][row][16 * col]) = vv[h];
       __syncthreads();
       {
         // K: thread (st, g, c) owns word st of owner 32 group + 4 g + c: tokens g
