@@ -116,6 +116,17 @@ def test_chunked_prefill_matches_fp32_causal_attention(kv_heads: int, group: int
     reqs.check(q, out, starts, third, group)
 
 
+def test_long_context_wraps_every_barrier_many_times() -> None:
+    """Twenty-odd pages per request: every ring slot, tile and barrier phase is reused many times."""
+    reqs = Requests(2, requests=2, max_tokens=3328, seed=29)
+    first = [2500, 1300]
+    q, out, starts = reqs.step(first, 2)
+    reqs.check(q, out, starts, first, 2)
+    second = [700, 1911]  # request 1 ends one token short of a block boundary
+    q, out, starts = reqs.step(second, 2)
+    reqs.check(q, out, starts, second, 2)
+
+
 def test_rejects_bad_arguments() -> None:
     reqs = Requests(2, requests=1, max_tokens=256, seed=3)
     tabs = RecordTables(*reqs.store.layer_tables(0))
@@ -127,3 +138,5 @@ def test_rejects_bad_arguments() -> None:
     q = torch.zeros(4, 4, D, dtype=torch.bfloat16, device=reqs.dev)
     with pytest.raises(RuntimeError):
         prefill_attention(q, tabs, reqs.block_table, one[:1], ctx, SCALE, torch.empty_like(q), 4)
+    with pytest.raises(RuntimeError):  # the kernel takes row maxima on the raw scores
+        prefill_attention(q, tabs, reqs.block_table, one, ctx, -SCALE, torch.empty_like(q), 4)
