@@ -183,3 +183,48 @@ def test_decode_attention_within_the_stated_tolerance(case) -> None:
                     q[b, h * G : (h + 1) * G].float().cpu(), kv[0][:, h], kv[1][:, h], SCALE
                 )
                 assert_attention_close(out[b, h * G : (h + 1) * G], ref, (name, layer, b, h))
+
+
+def test_back_to_back_launches_on_one_plan_keep_their_item_counters_apart(case) -> None:
+    """Many launches of the first-come-first-served schedule in flight on one plan.
+
+    Each attention launch since the plan was made draws its items from its own
+    counter, found from the order in which its CTAs arrive; consecutive
+    launches overlap (programmatic dependent launch), so a launch that drew
+    from a neighbour's counter would skip or repeat items.  Forty-eight
+    launches are queued without a synchronisation in between, each with its
+    own queries and output, and every output must equal, bit for bit, what the
+    same call returns when it runs alone on a fresh plan.
+    """
+    name, cfg, work = case
+    if name != "c3":
+        pytest.skip("the first-come-first-served schedule needs more (sequence, head) pairs than CTAs")
+    device = work.block_table.device
+    B, H, G = work.cfg.batch, work.cfg.kv_heads, work.cfg.group
+    sms = torch.cuda.get_device_properties(device).multi_processor_count
+    assert B * H > 2 * sms
+    units = decode_units(B, H, sms)
+    sizes = workspace_elems(H, units)
+    ws = (
+        torch.empty(sizes[0], device=device),
+        torch.empty(sizes[1], device=device),
+        torch.empty(sizes[2], dtype=torch.int32, device=device),
+    )
+    tabs = RecordTables(*work.store.layer_tables(0))
+    gen = torch.Generator(device=device).manual_seed(77)
+    launches = 48
+    qs = [torch.randn(B, H * G, 128, generator=gen, device=device).to(torch.bfloat16) for _ in range(launches)]
+    alone = []
+    for q in qs:
+        out = torch.full_like(q, float("nan"))
+        decode_attention(q, tabs, work.block_table, work.seq_lens, SCALE, units, out, ws, True)
+        torch.cuda.synchronize()
+        assert decode_status(ws, units) == 0
+        alone.append(out)
+    queued = [torch.full_like(q, float("nan")) for q in qs]
+    for i, (q, out) in enumerate(zip(qs, queued)):
+        decode_attention(q, tabs, work.block_table, work.seq_lens, SCALE, units, out, ws, i == 0)
+    torch.cuda.synchronize()
+    assert decode_status(ws, units) == 0
+    for i, (a, b) in enumerate(zip(alone, queued)):
+        assert torch.equal(a, b), f"launch {i} differs from the same call run alone"
