@@ -105,16 +105,18 @@ struct DecodeParams {
   int32_t* dyn;       // dynamic schedule words of the plan (see plan_words)
   int64_t q_stride;   // in 32-bit words
   int64_t bt_stride;  // in entries
-  int kvh, group, units;
+  int kvh, group, units, batch;
   float scale_log2;
   PipeConsts k;
   long long wait_limit;   // cycle budget of every bounded wait
   long long skip_record;  // test hook: ordinal of a record the producer leaves out (-1: none)
 };
 
-// Plan (int32): [0] pages per chunk, [1] units in use, [2 + 2u] sequence and
-// [3 + 2u] first page of unit u (sequence -1: idle), [2 + 2 units + 2 b] first
-// unit and [.. + 1] chunk count of sequence b, then one spare word and the
+// Plan (int32): [0] pages of the longest unit, [1] units in use, [2 + 2u]
+// sequence and [3 + 2u] first page | pages << 16 of unit u (sequence -1:
+// idle), [2 + 2 units + 2 b] first unit and [.. + 1] chunk count of sequence b,
+// behind them (if units >= 2 batch) the units listed by decreasing length,
+// then one word that says whether that list is there and the
 // status word, then the words of the dynamic item schedule (batches with more
 // (sequence, head) pairs than resident CTAs): the number of attention CTAs
 // started since the plan was made, and one item counter per attention launch
@@ -170,14 +172,18 @@ struct Item {
 };
 
 __device__ __forceinline__ bool load_item(const DecodeParams& p, int item, Item& it) {
-  it.unit = item / p.kvh;
-  it.head = item - it.unit * p.kvh;
+  // Items walk the planner's list of units by decreasing length (when the
+  // workspace had room for it), heads innermost.
+  const int place = item / p.kvh;
+  it.head = item - place * p.kvh;
+  it.unit = p.plan[status_index(p.units) - 1] ? p.plan[2 + 2 * p.units + 2 * p.batch + place] : place;
   it.seq_index = p.plan[2 + 2 * it.unit];
   if (it.seq_index < 0) return false;
-  it.first_page = p.plan[3 + 2 * it.unit];
+  const int where = p.plan[3 + 2 * it.unit];
+  it.first_page = where & 0xffff;
   it.seq_len = p.seq_lens[it.seq_index];
   const int total = (it.seq_len + 127) >> 7;
-  it.pages = max(0, min(total, it.first_page + p.plan[0]) - it.first_page);
+  it.pages = max(0, min(total - it.first_page, where >> 16));
   return it.pages > 0;
 }
 
@@ -268,7 +274,7 @@ __device__ __forceinline__ void produce(const DecodeParams& p, Smem<kCtas>& sm) 
             sm.desc[slot].addr = addr;
             sm.desc[slot].vlen = vlen;
             if (kDynamic) {
-              sm.desc[slot].item = item;
+              sm.desc[slot].item = it.unit * p.kvh + it.head;  // unit and head, not the place in the schedule
               sm.desc[slot].seq_index = it.seq_index;
               sm.desc[slot].first_page = it.first_page;
               sm.desc[slot].pages = it.pages;
@@ -672,7 +678,7 @@ __device__ __forceinline__ void plain_produce(const DecodeParams& p, PlainSmem& 
             const bool raw = vlen > kVarCap;
             sm.raw[slot] = raw;
             if (kDynamic) {
-              sm.desc[slot].item = item;
+              sm.desc[slot].item = it.unit * p.kvh + it.head;  // unit and head, not the place in the schedule
               sm.desc[slot].seq_index = it.seq_index;
               sm.desc[slot].first_page = it.first_page;
               sm.desc[slot].pages = it.pages;
@@ -1072,9 +1078,30 @@ __global__ void peer_wait_kernel(PeerFlags f) {
 }
 
 // ---------------------------------------------------------------------------
-// Planner: one CTA, once per step.  Picks the chunk length (pages per unit)
-// that minimises the static schedule's makespan on `slots` resident CTAs and
-// maps units to (sequence, first page).
+// Planner: one CTA, once per step.  Cuts the sequences into units (chunks of
+// consecutive pages), lists the units by decreasing length and maps them to
+// (sequence, first page, pages).  Both schedules walk that list, so a CTA's
+// items are one long, one medium, one short instead of whatever the sequence
+// order deals; and since the block scheduler deals CTAs breadth first (one per
+// SM per pass: CTA i, i + SMs, i + 2 SMs meet on one SM), so are an SM's.
+//
+// Sequences of one length (the usual padded decode batch): candidate t shares
+// t * SMs items out over the sequences - some get one chunk more than the
+// others - and cuts every sequence into equal chunks (a page apart at most).
+// There are at most four chunk lengths, so the makespan of the static walk is
+// known exactly: the first CTA takes the longest item of every round, the
+// first SM the longest of every pass; the cost is the larger of the two (an
+// SM's CTAs share its decode throughput), an item costing its pages plus about
+// three quarters of a page of start-up.
+//
+// Ragged batches: candidate k cuts the longest sequence into k chunks of ppc
+// pages and every sequence into chunks of at most ppc; rounds of the longest
+// item, or, first come first served, the even share plus one item.
+//
+// Plan words: [0] longest unit in pages, [1] units in use, then per unit
+// (sequence or -1, first page | pages << 16), then per sequence (first unit,
+// units), then - when the workspace has the room, units >= 2 * batch - the
+// list of units by decreasing length; [2 + 4 units] says whether it is there.
 // ---------------------------------------------------------------------------
 __device__ __forceinline__ int block_reduce_sum(int v, int* scratch) {
 #pragma unroll
@@ -1099,17 +1126,69 @@ __device__ __forceinline__ int block_reduce_max(int v, int* scratch) {
   return t;
 }
 
+// Exclusive prefix of `v` over the block; `total` receives the block's sum.
+__device__ __forceinline__ int block_exclusive_sum(int v, int* warp_total, int& total) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int before = warp_exclusive_sum(v, lane);
+  __syncthreads();
+  if (lane == 31) warp_total[warp] = before + v;
+  __syncthreads();
+  int first = before;
+  total = 0;
+#pragma unroll
+  for (int w = 0; w < kPlanThreads / 32; ++w) {
+    if (w < warp) first += warp_total[w];
+    total += warp_total[w];
+  }
+  return first;
+}
+
+constexpr int kMaxUnitPages = 1024;  // 131,072 tokens
+
+// A batch of `active` sequences of `n` pages cut into `target` units: `more`
+// sequences (the first ones) get `fewest + 1` chunks, the others `fewest`.
+struct EvenCut {
+  int fewest, more;
+};
+__device__ __forceinline__ EvenCut even_cut(int target, int active, int n) {
+  EvenCut c;
+  c.fewest = target / active;
+  c.more = target - c.fewest * active;
+  if (c.fewest >= n) {  // cannot cut finer than pages
+    c.fewest = n;
+    c.more = 0;
+  }
+  return c;
+}
+
+// Sum of the item costs (4 pages + 3) at ranks 0, bins, 2 bins, .. of the
+// items listed by decreasing length; `pages[x]` (decreasing) occurs `count[x]` times.
+__device__ __forceinline__ long long first_of_every_round(const int (&pages)[4], const long long (&count)[4],
+                                                          long long bins) {
+  long long sum = 0, start = 0;
+#pragma unroll
+  for (int x = 0; x < 4; ++x) {
+    const long long end = start + count[x];
+    // multiples of `bins` in [start, end)
+    const long long hits = (end + bins - 1) / bins - (start + bins - 1) / bins;
+    sum += hits * (4LL * pages[x] + 3);
+    start = end;
+  }
+  return sum;
+}
+
 __global__ void __launch_bounds__(kPlanThreads)
-plan_kernel(const int32_t* seq_lens, int32_t* plan, int batch, int units, int kvh, int slots,
+plan_kernel(const int32_t* seq_lens, int32_t* plan, int batch, int units, int kvh, int slots, int sms,
             int dynamic) {
   __shared__ int scratch[kPlanThreads / 32];
-  __shared__ unsigned long long best;
   __shared__ int warp_total[kPlanThreads / 32];
-  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  __shared__ unsigned long long best;
+  __shared__ int bins[kMaxUnitPages + 1];
+  const int tid = threadIdx.x;
   int total = 0, longest = 0, active = 0;
   int short_gap = 0;  // (1 << 30) - pages of the shortest sequence with context (0: none yet)
   for (int b = tid; b < batch; b += kPlanThreads) {
-    const int n = (seq_lens[b] + 127) >> 7;
+    const int n = min((seq_lens[b] + 127) >> 7, kMaxUnitPages);
     total += n;
     longest = max(longest, n);
     if (n > 0) short_gap = max(short_gap, (1 << 30) - n);
@@ -1119,73 +1198,146 @@ plan_kernel(const int32_t* seq_lens, int32_t* plan, int batch, int units, int kv
   longest = block_reduce_max(longest, scratch);
   short_gap = block_reduce_max(short_gap, scratch);
   active = block_reduce_sum(active, scratch);
-  // Sequences of one length cut into equal items: rounds of items, whoever takes them.
   const bool ragged = short_gap > 0 && (1 << 30) - short_gap != longest;
   // Each padding row gives back the unit reserved for it.
   const int capacity = max(1, units - batch + active);
   if (tid == 0) best = ~0ull;
+  for (int i = tid; i <= kMaxUnitPages; i += kPlanThreads) bins[i] = 0;
   __syncthreads();
-  // Candidate k cuts the longest sequence into k chunks.
-  {
+
+  if (active > 0 && !ragged) {
+    // Candidate 0: one chunk per sequence.  Candidate t: t * SMs items.
+    const long long target = tid == 0 ? active : (long long)tid * sms / kvh;
+    if (tid == 0 || (target > active && target <= capacity)) {
+      const int n = longest;
+      const EvenCut cut = even_cut((int)target, active, n);
+      // Chunk lengths, decreasing: sequences with `fewest` chunks have the
+      // longer ones; within a sequence `n mod chunks` chunks have a page more.
+      int pages[4];
+      long long count[4];
+      const int few = cut.fewest, many = min(cut.fewest + 1, n);
+      pages[1] = n / few;
+      pages[0] = pages[1] + 1;
+      count[0] = (long long)(active - cut.more) * (n - pages[1] * few) * kvh;
+      count[1] = (long long)(active - cut.more) * few * kvh - count[0];
+      pages[3] = n / many;
+      pages[2] = pages[3] + 1;
+      count[2] = (long long)cut.more * (n - pages[3] * many) * kvh;
+      count[3] = (long long)cut.more * many * kvh - count[2];
+      if (pages[2] > pages[1]) {  // n / many + 1 may exceed n / few only when they are equal
+        const int p = pages[1];
+        const long long c = count[1];
+        pages[1] = pages[2];
+        count[1] = count[2];
+        pages[2] = p;
+        count[2] = c;
+      }
+      const long long per_sm = slots / sms;
+      const unsigned long long cost =
+          (unsigned long long)max(first_of_every_round(pages, count, slots) * per_sm,
+                                  first_of_every_round(pages, count, sms));
+      // Ties go to the coarser cut (fewer partial results).
+      atomicMin(&best, (cost << 20) | (unsigned long long)tid);
+    }
+  } else if (active > 0) {
+    // Candidate k cuts the longest sequence into k chunks.
     const int ppc = max(1, (longest + tid) / (tid + 1));
     const float inv = 1.0f / (float)ppc;
     int chunks = 0;
     for (int b = 0; b < batch; ++b) {
       // ceil(pages / ppc) without an integer division: estimate, then correct.
-      const int up = ((seq_lens[b] + 127) >> 7) + ppc - 1;
+      const int up = min((seq_lens[b] + 127) >> 7, kMaxUnitPages) + ppc - 1;
       int q = (int)((float)up * inv);
       if (q * ppc > up) --q;
       if ((q + 1) * ppc <= up) ++q;
       chunks += q;
     }
     if (chunks <= capacity) {
-      // Costs in quarter pages.  Per item: ppc pages plus about three quarters
-      // of a page of start-up.  Equal items, or a static schedule: every CTA
-      // runs `rounds` items.  Ragged items taken first come, first served: the
-      // step ends within one item of the even share.
+      // Costs in quarter pages.  A static schedule: every CTA runs `rounds`
+      // items.  Ragged items taken first come, first served: the step ends
+      // within one item of the even share.
       const long long items = (long long)chunks * kvh;
       const long long rounds = max(1LL, (items + slots - 1) / slots);
       const long long one = 4LL * ppc + 3;
       const long long share = (4LL * total * kvh + 3 * items + slots - 1) / slots;
       const unsigned long long cost =
-          (unsigned long long)(dynamic && ragged && items > slots ? share + one : rounds * one);
+          (unsigned long long)(dynamic && items > slots ? share + one : rounds * one);
       // Ties go to the longer chunk (fewer partial results).
       atomicMin(&best, (cost << 20) | (unsigned long long)(0xfffff - ppc));
     }
   }
   __syncthreads();
-  const int ppc = (int)(0xfffff - (best & 0xfffff));
+  const int choice = (int)(best & 0xfffff);
+  const int ppc = 0xfffff - choice;  // ragged batches
+  const EvenCut cut = even_cut(!ragged && active > 0 ? (choice == 0 ? active : (int)((long long)choice * sms / kvh)) : 1,
+                               max(active, 1), max(longest, 1));
 
+  // Units, sequence by sequence; a sequence's chunks are consecutive units.
   int32_t* seq_plan = plan + 2 + 2 * units;
-  int used = 0;
+  int used = 0, seen = 0, top = 0;
   for (int base = 0; base < batch; base += kPlanThreads) {
     const int b = base + tid;
-    const int chunks = b < batch ? (((seq_lens[b] + 127) >> 7) + ppc - 1) / ppc : 0;
-    const int before = warp_exclusive_sum(chunks, lane);
-    if (lane == 31) warp_total[warp] = before + chunks;
-    __syncthreads();
-    int first = used + before, tile = 0;
-#pragma unroll
-    for (int w = 0; w < kPlanThreads / 32; ++w) {
-      if (w < warp) first += warp_total[w];
-      tile += warp_total[w];
-    }
+    const int n = b < batch ? min((seq_lens[b] + 127) >> 7, kMaxUnitPages) : 0;
+    int tile_active;
+    const int rank = seen + block_exclusive_sum(n > 0, warp_total, tile_active);  // among the active sequences
+    int chunks = 0;
+    if (n > 0) chunks = ragged ? (n + ppc - 1) / ppc : min(cut.fewest + (rank < cut.more), n);
+    int tile_units;
+    const int first = used + block_exclusive_sum(chunks, warp_total, tile_units);
     if (b < batch) {
       seq_plan[2 * b] = first;
       seq_plan[2 * b + 1] = chunks;
-      for (int s = 0; s < chunks; ++s) {
-        plan[2 + 2 * (first + s)] = b;
-        plan[3 + 2 * (first + s)] = s * ppc;
+      if (chunks > 0) {
+        // Ragged: chunks of ppc pages and a remainder.  Else equal chunks, the
+        // first `extra` of them a page longer.
+        const int small = ragged ? ppc : n / chunks;
+        const int extra = ragged ? 0 : n - small * chunks;
+        int page = 0;
+        for (int s = 0; s < chunks; ++s) {
+          const int pages = min(small + (s < extra), n - page);
+          plan[2 + 2 * (first + s)] = b;
+          plan[3 + 2 * (first + s)] = page | (pages << 16);
+          atomicAdd(&bins[pages], 1);
+          top = max(top, pages);
+          page += pages;
+        }
       }
     }
-    used += tile;
-    __syncthreads();
+    used += tile_units;
+    seen += tile_active;
   }
   for (int u = used + tid; u < units; u += kPlanThreads) plan[2 + 2 * u] = -1;
+  top = block_reduce_max(top, scratch);
+
+  // The list of units by decreasing length, behind the sequence table.
+  const bool listed = units >= 2 * batch;
+  if (listed) {
+    int32_t* order = seq_plan + 2 * batch;
+    // bins[p] -> place of the first unit of p pages; thread t scans the four
+    // lengths 1024 - 4 t .. 1021 - 4 t.
+    static_assert(kMaxUnitPages == 4 * kPlanThreads, "one thread scans four bins");
+    __syncthreads();
+    int count[4], mine = 0;
+#pragma unroll
+    for (int x = 0; x < 4; ++x) {
+      count[x] = bins[kMaxUnitPages - (4 * tid + x)];
+      mine += count[x];
+    }
+    int all;
+    int at = block_exclusive_sum(mine, warp_total, all);
+#pragma unroll
+    for (int x = 0; x < 4; ++x) {
+      bins[kMaxUnitPages - (4 * tid + x)] = at;
+      at += count[x];
+    }
+    __syncthreads();
+    for (int u = tid; u < used; u += kPlanThreads)
+      order[atomicAdd(&bins[plan[3 + 2 * u] >> 16], 1)] = u;
+  }
   if (tid == 0) {
-    plan[0] = ppc;
+    plan[0] = top;
     plan[1] = used;
-    plan[status_index(units) - 1] = 0;
+    plan[status_index(units) - 1] = listed ? 1 : 0;
     plan[status_index(units)] = 0;
   }
   for (int i = tid; i < kDynWords; i += kPlanThreads) plan[dyn_index(units) + i] = 0;
@@ -1286,7 +1438,7 @@ int launch_decode(bool plain, const fp_peers* peers, int buffer, const void* q, 
   // depends on the call's shape only, so all layers of a step agree.
   const bool dynamic = (long long)batch * kv_heads > slots;
   if (replan) {
-    plan_kernel<<<1, kPlanThreads, 0, st>>>(seq_lens, plan, batch, units, kv_heads, slots,
+    plan_kernel<<<1, kPlanThreads, 0, st>>>(seq_lens, plan, batch, units, kv_heads, slots, sms,
                                             dynamic ? 1 : 0);
     FP_LAUNCH_CHECK("plan_kernel");
   }
@@ -1308,6 +1460,7 @@ int launch_decode(bool plain, const fp_peers* peers, int buffer, const void* q, 
   p.kvh = kv_heads;
   p.group = group;
   p.units = units;
+  p.batch = batch;
   p.scale_log2 = scale * 1.4426950408889634f;
   p.k = pipe_consts();
   p.wait_limit = wait_debug().limit;
