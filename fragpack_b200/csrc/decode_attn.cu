@@ -1085,9 +1085,10 @@ __global__ void peer_wait_kernel(PeerFlags f) {
 // order deals; and since the block scheduler deals CTAs breadth first (one per
 // SM per pass: CTA i, i + SMs, i + 2 SMs meet on one SM), so are an SM's.
 //
-// Sequences of one length (the usual padded decode batch): candidate t shares
+// Sequences of one length (the usual padded decode batch): a candidate shares
 // t * SMs items out over the sequences - some get one chunk more than the
-// others - and cuts every sequence into equal chunks (a page apart at most).
+// others - or gives every sequence k chunks, and cuts every sequence into
+// equal chunks (a page apart at most).
 // There are at most four chunk lengths, so the makespan of the static walk is
 // known exactly: the first CTA takes the longest item of every round, the
 // first SM the longest of every pass; the cost is the larger of the two (an
@@ -1206,9 +1207,11 @@ plan_kernel(const int32_t* seq_lens, int32_t* plan, int batch, int units, int kv
   __syncthreads();
 
   if (active > 0 && !ragged) {
-    // Candidate 0: one chunk per sequence.  Candidate t: t * SMs items.
-    const long long target = tid == 0 ? active : (long long)tid * sms / kvh;
-    if (tid == 0 || (target > active && target <= capacity)) {
+    // Candidates: t * SMs items (threads 1 .. 127) and k chunks per sequence
+    // (threads 128 ..; k = 1 is the coarsest cut).
+    const long long target = tid < kPlanThreads / 2 ? (long long)tid * sms / kvh
+                                                    : (long long)(tid - kPlanThreads / 2 + 1) * active;
+    if (target >= active && target <= min(capacity, 0xfffff)) {
       const int n = longest;
       const EvenCut cut = even_cut((int)target, active, n);
       // Chunk lengths, decreasing: sequences with `fewest` chunks have the
@@ -1237,7 +1240,7 @@ plan_kernel(const int32_t* seq_lens, int32_t* plan, int batch, int units, int kv
           (unsigned long long)max(first_of_every_round(pages, count, slots) * per_sm,
                                   first_of_every_round(pages, count, sms));
       // Ties go to the coarser cut (fewer partial results).
-      atomicMin(&best, (cost << 20) | (unsigned long long)tid);
+      atomicMin(&best, (cost << 20) | (unsigned long long)target);
     }
   } else if (active > 0) {
     // Candidate k cuts the longest sequence into k chunks.
@@ -1269,8 +1272,7 @@ plan_kernel(const int32_t* seq_lens, int32_t* plan, int batch, int units, int kv
   __syncthreads();
   const int choice = (int)(best & 0xfffff);
   const int ppc = 0xfffff - choice;  // ragged batches
-  const EvenCut cut = even_cut(!ragged && active > 0 ? (choice == 0 ? active : (int)((long long)choice * sms / kvh)) : 1,
-                               max(active, 1), max(longest, 1));
+  const EvenCut cut = even_cut(!ragged && active > 0 ? choice : 1, max(active, 1), max(longest, 1));
 
   // Units, sequence by sequence; a sequence's chunks are consecutive units.
   int32_t* seq_plan = plan + 2 + 2 * units;
