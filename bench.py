@@ -26,7 +26,8 @@ BF16 read of the same logical KV.  With N = 1 the line also carries ``extra``:
 the same measurements on configurations 2 and 3 and the prefill side
 (token write, block encode, decompression) of configuration 4, at the nominal
 2 % junk and at the junk fraction that brings the overflow pool near its
-8192-record limit.
+8192-record limit, and prefill attention over the compressed records beside
+decompress-then-attend, at configuration 4's own size and on a small step.
 
 ``--impl reference`` runs the CPU pipeline alone (all host threads) as the
 reference arm; ``--impl reference-gpu`` and ``--arms`` select single arms;
@@ -1065,7 +1066,10 @@ def run_ours(args) -> dict:
         args.steps, args.warmup = keep
         extra["c4_prefill_as_written_junk_2pct"] = run_codec(args, 0.02)
         extra["c4_prefill_near_overflow_limit"] = run_codec(args, NEAR_LIMIT_JUNK)
-        extra["c4_prefill_attention"] = run_prefill_attention(args)
+        # Configuration 4's own size (16 requests of 8192 tokens: the last 2048-token
+        # chunk over 6144 cached tokens), and a small chunked-prefill step.
+        extra["c4_prefill_attention"] = run_prefill_attention(args, requests=16, cached=6144, chunk=2048)
+        extra["c4_prefill_attention_small"] = run_prefill_attention(args)
         line["extra"] = extra
     env.close()
     return line if env.rank == 0 else {}
