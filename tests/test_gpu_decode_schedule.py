@@ -239,3 +239,74 @@ def test_repeated_launches_are_bitwise_identical(encoded_store, units_policy: st
             first = out
         else:
             assert torch.equal(out.view(torch.int16), first.view(torch.int16))
+
+
+def _equal_lengths(batch: int, pages: int) -> np.ndarray:
+    lengths = np.full(batch, pages * TOKENS, np.int32)
+    lengths[3::5] = 0  # padding rows
+    return lengths
+
+
+@pytest.mark.parametrize(
+    "lengths_case",
+    ["ragged-17", "ragged-130", "equal-6x256", "equal-40x37", "equal-200x3", "one-long", "all-empty"],
+)
+def test_plan_cuts_every_sequence_once_and_lists_units_longest_first(encoded_store, lengths_case: str) -> None:
+    """The planner's words, read back: a partition of every sequence, and the order list.
+
+    Every sequence's pages are covered once by consecutive units in page order;
+    no unit is empty; padding rows have no unit; unused units are marked; and
+    the list both schedules walk is a permutation of the units in use with
+    non-increasing lengths.
+    """
+    store, _, _ = encoded_store
+    device = store.rec_addr.device
+    sms = torch.cuda.get_device_properties(device).multi_processor_count
+    if lengths_case.startswith("ragged"):
+        lengths = _ragged_lengths(int(lengths_case.split("-")[1]))
+    elif lengths_case.startswith("equal"):
+        batch, pages = map(int, lengths_case.split("-")[1].split("x"))
+        lengths = _equal_lengths(batch, pages)
+    elif lengths_case == "one-long":
+        lengths = np.array([MAX_PAGES * TOKENS], np.int32)
+    else:
+        lengths = np.zeros(9, np.int32)
+    batch = len(lengths)
+    units = decode_units(batch, HEADS, sms)
+    workspace = _workspace(units, device)
+    q = torch.zeros(batch, HEADS * GQA, DIM, dtype=torch.bfloat16, device=device)
+    out = torch.empty_like(q)
+    decode_attention(q, RecordTables(*store.layer_tables(0)), torch.from_numpy(_block_table(batch)).to(device),
+                     torch.from_numpy(lengths).to(device), SCALE, units, out, workspace, replan=True)
+    torch.cuda.synchronize()
+    assert decode_status(workspace, units) == 0
+    plan = workspace[2].cpu().numpy()
+    pages_of = (lengths.astype(np.int64) + TOKENS - 1) // TOKENS
+    used = int(plan[1])
+    assert 0 <= used <= units - batch + int((pages_of > 0).sum()) or used == 0
+    unit_seq = plan[2 : 2 + 2 * units : 2]
+    unit_where = plan[3 : 3 + 2 * units : 2]
+    assert (unit_seq[used:] == -1).all()
+    seq_plan = plan[2 + 2 * units : 2 + 2 * units + 2 * batch].reshape(batch, 2)
+    longest = 0
+    for b in range(batch):
+        first, chunks = map(int, seq_plan[b])
+        assert (chunks == 0) == (pages_of[b] == 0)
+        page = 0
+        for u in range(first, first + chunks):
+            assert unit_seq[u] == b
+            assert (int(unit_where[u]) & 0xFFFF) == page
+            count = int(unit_where[u]) >> 16
+            assert count > 0
+            longest = max(longest, count)
+            page += count
+        assert page == pages_of[b]
+    assert int(seq_plan[:, 1].sum()) == used
+    assert int(plan[0]) == longest
+    listed = int(plan[2 + 4 * units])
+    assert listed == int(units >= 2 * batch)
+    if listed:
+        order = plan[2 + 2 * units + 2 * batch : 2 + 2 * units + 2 * batch + used]
+        assert sorted(order.tolist()) == list(range(used))
+        sizes = unit_where[order] >> 16
+        assert (np.diff(sizes) <= 0).all()
