@@ -224,6 +224,9 @@ struct EncodeShared {
   // positions in ascending order; unused selectors are 8, which makes prmt
   // replicate the sign bit of an escape byte (always clear): a zero byte.
   uint32_t compact[256];
+  // The owners' low bytes, packed in store order, wait here from the
+  // classification to the final stores (sixteen registers less per thread).
+  __align__(16) uint4 park_low[4][kOwners];
   int warp_sum[2][8];
   uint8_t* dst;
   int raw;
@@ -290,7 +293,6 @@ __device__ __forceinline__ uint2 classes4(const EncodeShared& sh, uint32_t hi, c
 
 // What classification leaves in an owner's registers.
 struct OwnerCodes {
-  uint32_t low[16];   // low bytes, packed in store order
   uint32_t sym[6];    // symbol words
   uint64_t queue;     // first 16 escape nibbles
   uint32_t raw_q[4];  // first raw entries: local ordinal | high << 16
@@ -307,17 +309,18 @@ struct OwnerCodes {
 // (word st of the owner's record): a warp that meets such scalars in most of
 // its words then diverges once, not once per word.
 template <typename Reload>
-__device__ __forceinline__ void classify(const uint4 (&wd)[8], const EncodeShared& sh,
+__device__ __forceinline__ void classify(const uint4 (&wd)[8], EncodeShared& sh, int tid,
                                          const PipeConsts& k, OwnerCodes& o, Reload&& reload) {
-  uint32_t codes[8], marks[4];
+  uint32_t codes[8], marks[4], low[4];
   o.queue = 0;
   int n_esc = 0;
 #pragma unroll
   for (int st = 0; st < 8; ++st) {
     const uint32_t hi_a = __byte_perm(wd[st].x, wd[st].y, 0x7531);
     const uint32_t hi_b = __byte_perm(wd[st].z, wd[st].w, 0x7531);
-    o.low[2 * st] = __byte_perm(wd[st].x, wd[st].y, 0x6420);
-    o.low[2 * st + 1] = __byte_perm(wd[st].z, wd[st].w, 0x6420);
+    low[2 * (st & 1)] = __byte_perm(wd[st].x, wd[st].y, 0x6420);
+    low[2 * (st & 1) + 1] = __byte_perm(wd[st].z, wd[st].w, 0x6420);
+    if (st & 1) sh.park_low[st >> 1][tid] = make_uint4(low[0], low[1], low[2], low[3]);
     const uint2 ca = classes4(sh, hi_a, k), cb = classes4(sh, hi_b, k);
     codes[st] = prmt(ca.x, cb.x, 0x5410u);
     // Byte 0: which of the eight scalars escape; byte 1: which are outside the table.
@@ -493,7 +496,7 @@ __device__ __forceinline__ void encode_cta(const uint4 (&wd)[8], EncodeShared& s
   for (int i = tid; i < kVarCap / 16; i += kOwners)
     reinterpret_cast<uint4*>(sh.var)[i] = make_uint4(0, 0, 0, 0);
   OwnerCodes o;
-  classify(wd, sh, k, o, reload);
+  classify(wd, sh, tid, k, o, reload);
   const OwnerLayout at = record_layout(sh, o.n_esc, o.n_raw, tid);
   if (tid < 32) {
     bool raw = !at.plan.codes;
@@ -512,10 +515,8 @@ __device__ __forceinline__ void encode_cta(const uint4 (&wd)[8], EncodeShared& s
     for (int st = 0; st < 8; ++st) reinterpret_cast<uint4*>(dst)[st * kOwners + tid] = reload(st);
     return;
   }
-  const uint4 low[4] = {make_uint4(o.low[0], o.low[1], o.low[2], o.low[3]),
-                        make_uint4(o.low[4], o.low[5], o.low[6], o.low[7]),
-                        make_uint4(o.low[8], o.low[9], o.low[10], o.low[11]),
-                        make_uint4(o.low[12], o.low[13], o.low[14], o.low[15])};
+  const uint4 low[4] = {sh.park_low[0][tid], sh.park_low[1][tid], sh.park_low[2][tid],
+                        sh.park_low[3][tid]};
   const uint2 sym[3] = {make_uint2(o.sym[0], o.sym[1]), make_uint2(o.sym[2], o.sym[3]),
                         make_uint2(o.sym[4], o.sym[5])};
   store_dense(dst, low, sym, tid);
@@ -525,10 +526,12 @@ __device__ __forceinline__ void encode_cta(const uint4 (&wd)[8], EncodeShared& s
 
 // grid (max_close, 2 H): CTA (i, rec) encodes record `rec` of close_list[i]
 // at `layer` from staging.  hbm_kv.cu:257-429.
-// Four CTAs per SM (64 registers): the kernel's stalls are the load at a CTA's
-// start and the placement's atomic at its end, which only other resident CTAs
-// cover; a fourth CTA measured 12 % faster than three.
-__global__ void __launch_bounds__(kOwners, 4)
+// Five CTAs per SM (48 registers; the low bytes wait in shared memory instead
+// of sixteen registers): the kernel's stalls are the loads at a CTA's start
+// and the placement's atomic at its end, which only other resident CTAs cover.
+// A fourth CTA measured 12 % faster than three, the fifth 8 % faster again; a
+// sixth (40 registers, spills) is slower.
+__global__ void __launch_bounds__(kOwners, 5)
 encode_kernel(StoreView v, int layer, uint8_t* arena, int64_t page_bytes, const uint8_t* rank_of,
               PipeConsts k) {
   __shared__ EncodeShared sh;
