@@ -295,7 +295,8 @@ __device__ __forceinline__ uint2 classes4(const EncodeShared& sh, uint32_t hi, c
 struct OwnerCodes {
   uint32_t sym[6];    // symbol words
   uint64_t queue;     // first 16 escape nibbles
-  uint32_t raw_q[4];  // first raw entries: local ordinal | high << 16
+  // Bit 8 st + e of esc / raw: scalar e of word st escapes / is outside the table.
+  uint32_t esc[2], raw[2];
   int n_esc, n_raw;
 };
 
@@ -304,13 +305,13 @@ struct OwnerCodes {
 // are redone by build_variable_region).  `wd` is dead afterwards: the low bytes
 // are set aside in packed form as each word is consumed, so the 32 registers of
 // the record do not stay live to the end.  Scalars outside the table (raw
-// entries) are only marked while the words go by; their entries are made in
-// one short loop at the end, which fetches their high bytes with `reload(st)`
-// (word st of the owner's record): a warp that meets such scalars in most of
-// its words then diverges once, not once per word.
-template <typename Reload>
+// entries) are only marked while the words go by; build_variable_region makes
+// their entries, after the barrier at which the record's size becomes known,
+// so that the loop over them (lanes differ in how many they have, and each
+// fetches a high byte again) runs beside the placement's atomic instead of
+// holding every warp of the CTA up in front of that barrier.
 __device__ __forceinline__ void classify(const uint4 (&wd)[8], EncodeShared& sh, int tid,
-                                         const PipeConsts& k, OwnerCodes& o, Reload&& reload) {
+                                         const PipeConsts& k, OwnerCodes& o) {
   uint32_t codes[8], marks[4], low[4];
   o.queue = 0;
   int n_esc = 0;
@@ -341,27 +342,11 @@ __device__ __forceinline__ void classify(const uint4 (&wd)[8], EncodeShared& sh,
     if (n_esc < 16) o.queue |= (uint64_t)packed << (4 * n_esc);
     n_esc += __popc(mask8);
   }
-  // Bit 8 st + e of esc / raw: scalar e of word st escapes / is outside the table.
-  const uint32_t esc[2] = {prmt(marks[0], marks[1], 0x6420u), prmt(marks[2], marks[3], 0x6420u)};
-  uint32_t raw[2] = {prmt(marks[0], marks[1], 0x7531u), prmt(marks[2], marks[3], 0x7531u)};
-  const int n_raw = __popc(raw[0]) + __popc(raw[1]);
-#pragma unroll
-  for (int x = 0; x < 4; ++x) {
-    o.raw_q[x] = 0;
-    if (x < n_raw && n_raw <= 4) {
-      const int half = raw[0] ? 0 : 1;
-      const uint32_t m = raw[half];
-      const int bit = __ffs(m) - 1;
-      raw[half] = m & (m - 1);
-      const uint32_t below = (1u << bit) - 1u;
-      const int ordinal = half ? __popc(esc[0]) + __popc(esc[1] & below) : __popc(esc[0] & below);
-      const uint4 w = reload(4 * half + (bit >> 3));
-      const int e = bit & 7;
-      const uint32_t pair = e < 4 ? (e < 2 ? w.x : w.y) : (e < 6 ? w.z : w.w);
-      const uint32_t high = (pair >> (8 + 16 * (e & 1))) & 0xffu;
-      o.raw_q[x] = (uint32_t)ordinal | (high << 16);
-    }
-  }
+  o.esc[0] = prmt(marks[0], marks[1], 0x6420u);
+  o.esc[1] = prmt(marks[2], marks[3], 0x6420u);
+  o.raw[0] = prmt(marks[0], marks[1], 0x7531u);
+  o.raw[1] = prmt(marks[2], marks[3], 0x7531u);
+  const int n_raw = __popc(o.raw[0]) + __popc(o.raw[1]);
   o.n_esc = n_esc;
   o.n_raw = n_raw;
   // Symbol words: per 32-scalar group three words; bit 3 of word b's nibble j
@@ -432,10 +417,26 @@ __device__ __forceinline__ void build_variable_region(EncodeShared& sh, const Ow
     if (hi) atomicOr(&var32[word + 2], hi);
   }
   if (o.n_raw > 0 && o.n_raw <= 4 && o.n_esc <= 16) {
-    // Raw entries `ordinal | high << 16` (attn_page.py:188-191) from the queue.
+    // Raw entries `ordinal | high << 16` (attn_page.py:188-191): the ordinal
+    // from the masks, the high byte from the record's word again.
+    uint32_t left[2] = {o.raw[0], o.raw[1]};
 #pragma unroll
-    for (int x = 0; x < 4; ++x)
-      if (x < o.n_raw) var32[(at.raw_offset >> 2) + at.raw_at + x] = o.raw_q[x] + (uint32_t)at.esc_at;
+    for (int x = 0; x < 4; ++x) {
+      if (x < o.n_raw) {
+        const int half = left[0] ? 0 : 1;
+        const uint32_t m = left[half];
+        const int bit = __ffs(m) - 1;
+        left[half] = m & (m - 1);
+        const uint32_t below = (1u << bit) - 1u;
+        const int ordinal =
+            half ? __popc(o.esc[0]) + __popc(o.esc[1] & below) : __popc(o.esc[0] & below);
+        const uint4 w = reload(4 * half + (bit >> 3));
+        const int e = bit & 7;
+        const uint32_t pair = e < 4 ? (e < 2 ? w.x : w.y) : (e < 6 ? w.z : w.w);
+        const uint32_t high = (pair >> (8 + 16 * (e & 1))) & 0xffu;
+        var32[(at.raw_offset >> 2) + at.raw_at + x] = (uint32_t)(at.esc_at + ordinal) | (high << 16);
+      }
+    }
   }
   if (o.n_esc > 16 || o.n_raw > 4) {
     // Rare: walk the scalars again.
@@ -496,7 +497,7 @@ __device__ __forceinline__ void encode_cta(const uint4 (&wd)[8], EncodeShared& s
   for (int i = tid; i < kVarCap / 16; i += kOwners)
     reinterpret_cast<uint4*>(sh.var)[i] = make_uint4(0, 0, 0, 0);
   OwnerCodes o;
-  classify(wd, sh, tid, k, o, reload);
+  classify(wd, sh, tid, k, o);
   const OwnerLayout at = record_layout(sh, o.n_esc, o.n_raw, tid);
   if (tid < 32) {
     bool raw = !at.plan.codes;
