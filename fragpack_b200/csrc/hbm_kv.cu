@@ -100,12 +100,17 @@ __device__ __forceinline__ void scatter_token_row(uint8_t* k_rec, uint8_t* v_rec
   }
 }
 
+// 16 bytes global -> shared without a register in between.
+__device__ __forceinline__ void async_copy16(void* dst, const void* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_addr(dst)), "l"(src) : "memory");
+}
+
 __global__ void __launch_bounds__(256)
 write_kernel(StoreView v, const uint16_t* key, const uint16_t* value, int64_t ks0, int64_t ks1,
              int64_t vs0, int64_t vs1, const int64_t* slots, int64_t n_tokens, int layer,
              int vector_ok) {
   const fp_store& s = v.s;
-  __shared__ __align__(16) uint8_t tile[2][16][kWriteRow];
+  __shared__ __align__(16) uint8_t tile[kWriteHeads][2][16][kWriteRow];
   __shared__ int tok_slot[16];   // staging slot of each token, -1: skip the token
   __shared__ int tok_off[16];    // offset of each token in its block
   __shared__ int tok_flags[16];  // bit 0: covered by a complete group, bit 1: starts one
@@ -152,35 +157,34 @@ write_kernel(StoreView v, const uint16_t* key, const uint16_t* value, int64_t ks
     if (!(tok_flags[k] & 2)) continue;
     const int w = tok_slot[k], group = tok_off[k] >> 4;
     const int64_t first = t0 + k;
-    // All of the CTA's heads are fetched before the first is transposed: the
-    // loads of four heads (64 KB per CTA) are in flight together instead of one
-    // head's between two barriers.
+    // All of the CTA's heads are copied into shared memory before the first is
+    // transposed, asynchronously and without passing through registers: the
+    // loads of four heads (64 KB per CTA) are in flight together, the CTA meets
+    // at two barriers per group, and the kernel stays small in registers.
     const int row = tid >> 4, col = tid & 15;  // 16 tokens x 16 chunks of 16 bytes
-    uint4 kk[kWriteHeads], vv[kWriteHeads];
+    __syncthreads();  // the previous group's tiles have been read
 #pragma unroll
     for (int h = 0; h < kWriteHeads; ++h)
       if (h < heads) {
         const int head = head0 + h;
-        kk[h] = *reinterpret_cast<const uint4*>(key + (first + row) * ks0 + head * ks1 + 8 * col);
-        vv[h] = *reinterpret_cast<const uint4*>(value + (first + row) * vs0 + head * vs1 + 8 * col);
+        async_copy16(&tile[h][0][row][16 * col], key + (first + row) * ks0 + head * ks1 + 8 * col);
+        async_copy16(&tile[h][1][row][16 * col], value + (first + row) * vs0 + head * vs1 + 8 * col);
       }
+    asm volatile("cp.async.wait_all;" ::: "memory");
+    __syncthreads();
 #pragma unroll
     for (int h = 0; h < kWriteHeads; ++h) {
       if (h >= heads) break;
       const int head = head0 + h;
-      __syncthreads();  // the previous tile has been read
-      *reinterpret_cast<uint4*>(&tile[0][row][16 * col]) = kk[h];
-      *reinterpret_cast<uint4*>(&tile[1][row][16 * col]) = vv[h];
-      __syncthreads();
       {
         // K: thread (st, g, c) owns word st of owner 32 group + 4 g + c: tokens g
         // and g + 8, dim pairs 16 st + 2 c and + 8.
         const int st = tid >> 5, g = (tid >> 2) & 7, c = tid & 3;
         uint4 out;
-        out.x = *reinterpret_cast<const uint32_t*>(&tile[0][g][2 * (16 * st + 2 * c)]);
-        out.y = *reinterpret_cast<const uint32_t*>(&tile[0][g][2 * (16 * st + 8 + 2 * c)]);
-        out.z = *reinterpret_cast<const uint32_t*>(&tile[0][g + 8][2 * (16 * st + 2 * c)]);
-        out.w = *reinterpret_cast<const uint32_t*>(&tile[0][g + 8][2 * (16 * st + 8 + 2 * c)]);
+        out.x = *reinterpret_cast<const uint32_t*>(&tile[h][0][g][2 * (16 * st + 2 * c)]);
+        out.y = *reinterpret_cast<const uint32_t*>(&tile[h][0][g][2 * (16 * st + 8 + 2 * c)]);
+        out.z = *reinterpret_cast<const uint32_t*>(&tile[h][0][g + 8][2 * (16 * st + 2 * c)]);
+        out.w = *reinterpret_cast<const uint32_t*>(&tile[h][0][g + 8][2 * (16 * st + 8 + 2 * c)]);
         uint8_t* rec = v.staging(w, layer, head);
         *reinterpret_cast<uint4*>(rec + 16 * (kOwners * st + 32 * group + (tid & 31))) = out;
       }
@@ -194,8 +198,8 @@ write_kernel(StoreView v, const uint16_t* key, const uint16_t* value, int64_t ks
 #pragma unroll
           for (int f = 0; f < 2; ++f) {
             const int dim = 16 * dw + 8 * b + dg, tok = 8 * f + 2 * vc;
-            const uint32_t lo = *reinterpret_cast<const uint16_t*>(&tile[1][tok][2 * dim]);
-            const uint32_t hi = *reinterpret_cast<const uint16_t*>(&tile[1][tok + 1][2 * dim]);
+            const uint32_t lo = *reinterpret_cast<const uint16_t*>(&tile[h][1][tok][2 * dim]);
+            const uint32_t hi = *reinterpret_cast<const uint16_t*>(&tile[h][1][tok + 1][2 * dim]);
             out[2 * b + f] = lo | (hi << 16);
           }
         uint8_t* rec = v.staging(w, layer, s.H + head);
