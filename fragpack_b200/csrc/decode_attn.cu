@@ -115,8 +115,7 @@ struct DecodeParams {
 // Plan (int32): [0] pages of the longest unit, [1] units in use, [2 + 2u]
 // sequence and [3 + 2u] first page | pages << 16 of unit u (sequence -1:
 // idle), [2 + 2 units + 2 b] first unit and [.. + 1] chunk count of sequence b,
-// behind them (if units >= 2 batch) the units listed by decreasing length,
-// then one word that says whether that list is there and the
+// then one spare word and the
 // status word, then the words of the dynamic item schedule (batches with more
 // (sequence, head) pairs than resident CTAs): the number of attention CTAs
 // started since the plan was made, and one item counter per attention launch
@@ -128,7 +127,12 @@ constexpr int kMaxPlanLaunches = 256;  // launches per plan that are scheduled d
 constexpr int kDynWords = 4 + kMaxPlanLaunches;
 __host__ __device__ __forceinline__ int64_t status_index(int units) { return 2 + 4LL * units + 1; }
 __host__ __device__ __forceinline__ int64_t dyn_index(int units) { return status_index(units) + 1; }
-__host__ __device__ __forceinline__ int64_t plan_words(int units) { return dyn_index(units) + kDynWords; }
+// Behind them, 16-byte aligned: one descriptor per unit in the order in which
+// the schedules hand the units out (sequence, first page | pages << 16,
+// sequence length, unit), so that an item's start costs one load.
+__host__ __device__ __forceinline__ int64_t desc_index(int units) { return dyn_index(units) + kDynWords; }
+__host__ __device__ __forceinline__ int64_t plan_words(int units) { return desc_index(units) + 4LL * units; }
+static_assert((2 + 2 + kDynWords) % 4 == 0, "the unit descriptors must start on a 16-byte boundary");
 
 __device__ __forceinline__ void consumer_barrier() {
   asm volatile("bar.sync 1, %0;" ::"n"(kConsumers) : "memory");
@@ -172,18 +176,17 @@ struct Item {
 };
 
 __device__ __forceinline__ bool load_item(const DecodeParams& p, int item, Item& it) {
-  // Items walk the planner's list of units by decreasing length (when the
-  // workspace had room for it), heads innermost.
+  // Items walk the planner's list of units by decreasing length, heads innermost.
   const int place = item / p.kvh;
   it.head = item - place * p.kvh;
-  it.unit = p.plan[status_index(p.units) - 1] ? p.plan[2 + 2 * p.units + 2 * p.batch + place] : place;
-  it.seq_index = p.plan[2 + 2 * it.unit];
+  const int4 d = reinterpret_cast<const int4*>(p.plan + desc_index(p.units))[place];
+  it.seq_index = d.x;
   if (it.seq_index < 0) return false;
-  const int where = p.plan[3 + 2 * it.unit];
-  it.first_page = where & 0xffff;
-  it.seq_len = p.seq_lens[it.seq_index];
+  it.first_page = d.y & 0xffff;
+  it.seq_len = d.z;
+  it.unit = d.w;
   const int total = (it.seq_len + 127) >> 7;
-  it.pages = max(0, min(total - it.first_page, where >> 16));
+  it.pages = max(0, min(total - it.first_page, d.y >> 16));
   return it.pages > 0;
 }
 
@@ -1101,8 +1104,8 @@ __global__ void peer_wait_kernel(PeerFlags f) {
 //
 // Plan words: [0] longest unit in pages, [1] units in use, then per unit
 // (sequence or -1, first page | pages << 16), then per sequence (first unit,
-// units), then - when the workspace has the room, units >= 2 * batch - the
-// list of units by decreasing length; [2 + 4 units] says whether it is there.
+// units); behind the status and schedule words the units again, by decreasing
+// length, as (sequence, first page | pages << 16, sequence length, unit).
 // ---------------------------------------------------------------------------
 __device__ __forceinline__ int block_reduce_sum(int v, int* scratch) {
 #pragma unroll
@@ -1311,14 +1314,11 @@ plan_kernel(const int32_t* seq_lens, int32_t* plan, int batch, int units, int kv
   for (int u = used + tid; u < units; u += kPlanThreads) plan[2 + 2 * u] = -1;
   top = block_reduce_max(top, scratch);
 
-  // The list of units by decreasing length, behind the sequence table.
-  const bool listed = units >= 2 * batch;
-  if (listed) {
-    int32_t* order = seq_plan + 2 * batch;
-    // bins[p] -> place of the first unit of p pages; thread t scans the four
-    // lengths 1024 - 4 t .. 1021 - 4 t.
-    static_assert(kMaxUnitPages == 4 * kPlanThreads, "one thread scans four bins");
-    __syncthreads();
+  // The units by decreasing length: bins[p] -> place of the first unit of p
+  // pages; thread t scans the four lengths 1024 - 4 t .. 1021 - 4 t.
+  static_assert(kMaxUnitPages == 4 * kPlanThreads, "one thread scans four bins");
+  __syncthreads();
+  {
     int count[4], mine = 0;
 #pragma unroll
     for (int x = 0; x < 4; ++x) {
@@ -1332,14 +1332,18 @@ plan_kernel(const int32_t* seq_lens, int32_t* plan, int batch, int units, int kv
       bins[kMaxUnitPages - (4 * tid + x)] = at;
       at += count[x];
     }
-    __syncthreads();
-    for (int u = tid; u < used; u += kPlanThreads)
-      order[atomicAdd(&bins[plan[3 + 2 * u] >> 16], 1)] = u;
   }
+  __syncthreads();
+  int4* desc = reinterpret_cast<int4*>(plan + desc_index(units));
+  for (int u = tid; u < used; u += kPlanThreads) {
+    const int b = plan[2 + 2 * u], where = plan[3 + 2 * u];
+    desc[atomicAdd(&bins[where >> 16], 1)] = make_int4(b, where, seq_lens[b], u);
+  }
+  for (int u = used + tid; u < units; u += kPlanThreads) desc[u] = make_int4(-1, 0, 0, 0);
   if (tid == 0) {
     plan[0] = top;
     plan[1] = used;
-    plan[status_index(units) - 1] = listed ? 1 : 0;
+    plan[status_index(units) - 1] = 0;
     plan[status_index(units)] = 0;
   }
   for (int i = tid; i < kDynWords; i += kPlanThreads) plan[dyn_index(units) + i] = 0;
@@ -1417,7 +1421,7 @@ int launch_decode(bool plain, const fp_peers* peers, int buffer, const void* q, 
              "decode workspace too small");
   FP_REQUIRE(plan_elems >= plan_words(units), "decode plan must hold %lld int32",
              (long long)plan_words(units));
-  FP_REQUIRE(reinterpret_cast<uintptr_t>(plan) % 8 == 0 &&
+  FP_REQUIRE(reinterpret_cast<uintptr_t>(plan) % 16 == 0 &&
                  reinterpret_cast<uintptr_t>(opart) % 16 == 0 &&
                  reinterpret_cast<uintptr_t>(ml) % 8 == 0,
              "decode workspace must be 16-byte aligned");
@@ -1601,7 +1605,7 @@ constexpr int kStaticUnits = 4096;      // largest units served
 constexpr size_t kStaticOpartBytes = (size_t)kStaticUnitHeads * 8 * 128 * sizeof(float);
 constexpr size_t kStaticMlBytes = (size_t)kStaticUnitHeads * 8 * 2 * sizeof(float);
 constexpr size_t kStaticPlanBytes =
-    ((2 + 4 * (size_t)kStaticUnits + 2 + kDynWords) * sizeof(int32_t) + 255) / 256 * 256;
+    ((2 + 4 * (size_t)kStaticUnits + 2 + kDynWords + 4 * (size_t)kStaticUnits) * sizeof(int32_t) + 255) / 256 * 256;
 constexpr size_t kStaticScratchBytes = kStaticOpartBytes + kStaticMlBytes + kStaticPlanBytes;
 
 // In host code this name is only a handle for cudaGetSymbolAddress; it is not

@@ -17,9 +17,9 @@ the overflow pool in ``counters[13]``, which the reference leaves unused.
 
 Differences a caller of the reference's Python sees: none in results.
 ``workspace_elems`` of the reference sizes ``plan`` as ``2 + 4 * units`` int32;
-this library needs ``2 + 4 * units + 262`` (a spare, a status word and the
-words of its item schedule), so :func:`plan_words` must be used for that
-allocation.
+this library needs ``2 + 8 * units + 262`` (a spare, a status word, the words
+of its item schedule and four words per unit of item descriptors), so
+:func:`plan_words` must be used for that allocation.
 """
 
 from __future__ import annotations
@@ -54,7 +54,7 @@ class _Store(ctypes.Structure):
 
 def plan_words(units: int) -> int:
     """int32 elements of the decode ``plan`` workspace for ``units`` work units."""
-    return 2 + 4 * units + 2 + 260
+    return 2 + 4 * units + 2 + 260 + 4 * units
 
 
 def _p(t: torch.Tensor | None) -> ctypes.c_void_p:

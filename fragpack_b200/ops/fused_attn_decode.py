@@ -84,8 +84,9 @@ def decode_units(batch: int, kv_heads: int, num_sms: int) -> int:
 def workspace_elems(kv_heads: int, units: int) -> tuple[int, int, int]:
     """Return the element counts of the ``(opart, ml, plan)`` workspace.
 
-    Reference: ``fused_attn_decode.py:88-102``.  The plan holds two more words
-    than the reference's: a spare and the status word.
+    Reference: ``fused_attn_decode.py:88-102``.  The plan holds more than the
+    reference's: a spare and the status word, the words of the dynamic item
+    schedule, and four words per unit of item descriptors in schedule order.
 
     Args:
         kv_heads: KV heads per sequence.
@@ -95,7 +96,7 @@ def workspace_elems(kv_heads: int, units: int) -> tuple[int, int, int]:
         Float elements of ``opart`` and ``ml``, int32 elements of ``plan``.
     """
     rows = kv_heads * units * GQA
-    return rows * 128, rows * 2, 2 + 4 * units + 2 + _PLAN_SCHEDULE_WORDS
+    return rows * 128, rows * 2, 2 + 4 * units + 2 + _PLAN_SCHEDULE_WORDS + 4 * units
 
 
 @functools.cache

@@ -117,12 +117,13 @@ int fp_decode_workspace(int32_t kv_heads, int32_t units, int64_t* opart_elems, i
  *   group        query heads per KV head: 1, 2, 4 or 8
  *   units        work-unit capacity per KV head, >= B
  *   replan       nonzero: recompute the plan from seq_lens (first layer of a step)
- * `plan` holds 2 + 4 * units + 2 + 260 int32 (fp_decode_workspace gives the
- * count): the reference's plan, a spare word, a status word and the words of
- * the dynamic item schedule.  The int32 at index 2 + 4 * units + 1 is the status word: the
+ * `plan` holds 2 + 4 * units + 2 + 260 + 4 * units int32 (fp_decode_workspace
+ * gives the count): the reference's plan, a spare word, a status word, the
+ * words of the dynamic item schedule and four words per unit of item
+ * descriptors.  The int32 at index 2 + 4 * units + 1 is the status word: the
  * kernels OR FP_DECODE_* bits into it when a bounded device-side wait ran out
- * (results are then invalid); the planner clears it.  opart must be 16-byte
- * aligned, ml and plan 8-byte aligned.
+ * (results are then invalid); the planner clears it.  opart and plan must be
+ * 16-byte aligned, ml 8-byte aligned.
  */
 int fp_fused_decode(const void* q, int64_t q_stride, const int64_t* rec_addr,
                     const int32_t* rec_len, const int32_t* plut, const uint8_t* slut,

@@ -252,12 +252,13 @@ def _equal_lengths(batch: int, pages: int) -> np.ndarray:
     ["ragged-17", "ragged-130", "equal-6x256", "equal-40x37", "equal-200x3", "one-long", "all-empty"],
 )
 def test_plan_cuts_every_sequence_once_and_lists_units_longest_first(encoded_store, lengths_case: str) -> None:
-    """The planner's words, read back: a partition of every sequence, and the order list.
+    """The planner's words, read back: a partition of every sequence, and the item descriptors.
 
     Every sequence's pages are covered once by consecutive units in page order;
     no unit is empty; padding rows have no unit; unused units are marked; and
-    the list both schedules walk is a permutation of the units in use with
-    non-increasing lengths.
+    the item descriptors both schedules walk are a permutation of the units in
+    use with non-increasing lengths, each repeating its unit's entry and its
+    sequence's length.
     """
     store, _, _ = encoded_store
     device = store.rec_addr.device
@@ -303,10 +304,12 @@ def test_plan_cuts_every_sequence_once_and_lists_units_longest_first(encoded_sto
         assert page == pages_of[b]
     assert int(seq_plan[:, 1].sum()) == used
     assert int(plan[0]) == longest
-    listed = int(plan[2 + 4 * units])
-    assert listed == int(units >= 2 * batch)
-    if listed:
-        order = plan[2 + 2 * units + 2 * batch : 2 + 2 * units + 2 * batch + used]
-        assert sorted(order.tolist()) == list(range(used))
-        sizes = unit_where[order] >> 16
-        assert (np.diff(sizes) <= 0).all()
+    # The item descriptors, in the order the schedules hand the units out.
+    first_desc = 2 + 4 * units + 2 + 4 + 256
+    desc = plan[first_desc : first_desc + 4 * units].reshape(units, 4)
+    assert sorted(desc[:used, 3].tolist()) == list(range(used))
+    assert (desc[used:, 0] == -1).all()
+    assert (np.diff(desc[:used, 1] >> 16) <= 0).all()
+    for place in range(used):
+        seq, where, length, unit = map(int, desc[place])
+        assert seq == unit_seq[unit] and where == unit_where[unit] and length == lengths[seq]

@@ -115,8 +115,9 @@ def test_layout_arithmetic() -> None:
     assert fad.decode_units(4, 4, 148) == 4 + fad.SPLIT_WAVES * 74 - 1
     assert fad.decode_units(3, 0, 148) >= 3
     opart, ml, plan = fad.workspace_elems(4, 77)
-    # plan: header, unit and sequence tables, spare + status words, then the dynamic schedule words
-    assert (opart, ml, plan) == (4 * 77 * 8 * 128, 4 * 77 * 8 * 2, 2 + 4 * 77 + 2 + 4 + 256)
+    # plan: header, unit and sequence tables, spare + status words, the dynamic schedule words,
+    # then four words per unit of item descriptors
+    assert (opart, ml, plan) == (4 * 77 * 8 * 128, 4 * 77 * 8 * 2, 2 + 4 * 77 + 2 + 4 + 256 + 4 * 77)
     assert ap.blob_head_bytes(2, 2) == 4096
     assert ap.blob_slot_bytes(2, 2) == 4096 + 2 * 2 * 2 * 32768
     assert ap.blob_head_bytes(80, 8) == -(-(64 + 8 * 80 * 8) // 4096) * 4096
