@@ -249,7 +249,8 @@ def _equal_lengths(batch: int, pages: int) -> np.ndarray:
 
 @pytest.mark.parametrize(
     "lengths_case",
-    ["ragged-17", "ragged-130", "equal-6x256", "equal-40x37", "equal-200x3", "one-long", "all-empty"],
+    ["ragged-17", "ragged-130", "ragged-700", "equal-6x256", "equal-40x37", "equal-200x3", "equal-600x5",
+     "one-long", "all-empty"],
 )
 def test_plan_cuts_every_sequence_once_and_lists_units_longest_first(encoded_store, lengths_case: str) -> None:
     """The planner's words, read back: a partition of every sequence, and the item descriptors.
