@@ -1147,7 +1147,9 @@ __device__ __forceinline__ int block_exclusive_sum(int v, int* warp_total, int& 
   return first;
 }
 
-constexpr int kMaxUnitPages = 1024;  // 131,072 tokens
+// Units are sorted by length up to this many pages (131,072 tokens); longer
+// ones - contexts beyond what the reference's tests reach - share the last bin.
+constexpr int kMaxUnitPages = 1024;
 
 // A batch of `active` sequences of `n` pages cut into `target` units: `more`
 // sequences (the first ones) get `fewest + 1` chunks, the others `fewest`.
@@ -1192,7 +1194,7 @@ plan_kernel(const int32_t* seq_lens, int32_t* plan, int batch, int units, int kv
   int total = 0, longest = 0, active = 0;
   int short_gap = 0;  // (1 << 30) - pages of the shortest sequence with context (0: none yet)
   for (int b = tid; b < batch; b += kPlanThreads) {
-    const int n = min((seq_lens[b] + 127) >> 7, kMaxUnitPages);
+    const int n = (seq_lens[b] + 127) >> 7;
     total += n;
     longest = max(longest, n);
     if (n > 0) short_gap = max(short_gap, (1 << 30) - n);
@@ -1252,7 +1254,7 @@ plan_kernel(const int32_t* seq_lens, int32_t* plan, int batch, int units, int kv
     int chunks = 0;
     for (int b = 0; b < batch; ++b) {
       // ceil(pages / ppc) without an integer division: estimate, then correct.
-      const int up = min((seq_lens[b] + 127) >> 7, kMaxUnitPages) + ppc - 1;
+      const int up = ((seq_lens[b] + 127) >> 7) + ppc - 1;
       int q = (int)((float)up * inv);
       if (q * ppc > up) --q;
       if ((q + 1) * ppc <= up) ++q;
@@ -1282,7 +1284,7 @@ plan_kernel(const int32_t* seq_lens, int32_t* plan, int batch, int units, int kv
   int used = 0, seen = 0, top = 0;
   for (int base = 0; base < batch; base += kPlanThreads) {
     const int b = base + tid;
-    const int n = b < batch ? min((seq_lens[b] + 127) >> 7, kMaxUnitPages) : 0;
+    const int n = b < batch ? (seq_lens[b] + 127) >> 7 : 0;
     int tile_active;
     const int rank = seen + block_exclusive_sum(n > 0, warp_total, tile_active);  // among the active sequences
     int chunks = 0;
@@ -1302,7 +1304,7 @@ plan_kernel(const int32_t* seq_lens, int32_t* plan, int batch, int units, int kv
           const int pages = min(small + (s < extra), n - page);
           plan[2 + 2 * (first + s)] = b;
           plan[3 + 2 * (first + s)] = page | (pages << 16);
-          atomicAdd(&bins[pages], 1);
+          atomicAdd(&bins[min(pages, kMaxUnitPages)], 1);
           top = max(top, pages);
           page += pages;
         }
@@ -1337,7 +1339,7 @@ plan_kernel(const int32_t* seq_lens, int32_t* plan, int batch, int units, int kv
   int4* desc = reinterpret_cast<int4*>(plan + desc_index(units));
   for (int u = tid; u < used; u += kPlanThreads) {
     const int b = plan[2 + 2 * u], where = plan[3 + 2 * u];
-    desc[atomicAdd(&bins[where >> 16], 1)] = make_int4(b, where, seq_lens[b], u);
+    desc[atomicAdd(&bins[min(where >> 16, kMaxUnitPages)], 1)] = make_int4(b, where, seq_lens[b], u);
   }
   for (int u = used + tid; u < units; u += kPlanThreads) desc[u] = make_int4(-1, 0, 0, 0);
   if (tid == 0) {
@@ -1385,6 +1387,8 @@ int launch_decode(bool plain, const fp_peers* peers, int buffer, const void* q, 
   FP_REQUIRE(group == 1 || group == 2 || group == 4 || group == 8,
              "query group %d must be 1, 2, 4 or 8", group);
   FP_REQUIRE(units >= batch, "decode needs at least one unit per sequence");
+  // A unit's first page and page count are packed into 16 bits each in the plan.
+  FP_REQUIRE(bt_stride <= 32767, "block tables of more than 32767 pages per sequence are not supported");
   FP_REQUIRE((int64_t)kv_heads * units * 8 < (1LL << 31), "kv_heads * units too large");
   FP_REQUIRE(q && rec_addr && rec_len && (plain || (plut && slut)) && block_table && seq_lens &&
                  opart && ml && plan && (out || peers),
