@@ -1044,7 +1044,8 @@ def run_ours(args) -> dict:
         line = run_codec(args, args.junk if args.junk >= 0 else NEAR_LIMIT_JUNK, args.layers or 2)
         line.update({"metric": "block_encode_and_decompress_throughput", "n_gpus": 1})
         if args.prefill_attention:
-            line["prefill_attention"] = run_prefill_attention(args)
+            shape = [int(x) for x in args.prefill_shape.split(",")]
+            line["prefill_attention"] = run_prefill_attention(args, *shape)
         clocks.stop()
         env.close()
         return line
@@ -1167,6 +1168,8 @@ def main() -> None:
     parser.add_argument("--codec-steps", type=int, default=5, help="c4: timed passes over the layers")
     parser.add_argument("--prefill-attention", action="store_true",
                         help="c4: also time prefill attention over compressed records")
+    parser.add_argument("--prefill-shape", default="4,2048,512",
+                        help="c4 --prefill-attention: requests,cached tokens,new tokens")
     parser.add_argument("--gather", choices=("peers", "nccl"), default="peers",
                         help="N > 1: how the per-rank outputs reach every rank's o_proj input")
     parser.add_argument("--layers", type=int, default=0, help="resident layers (default: what fits)")
